@@ -16,11 +16,11 @@ from .ops import (  # noqa: F401
     rope_bwd,
     rope_fwd,
 )
-from .attention import AttnParams, attn_bwd, attn_fwd, attention  # noqa: F401
+from .attention import AttnParams, attn_bwd, attn_fwd, attention, check_device_status  # noqa: F401
 from .sharding import shard_units  # noqa: F401
 
 __all__ = [
     "ROPE_BASE", "GPTConfig", "precompute_rope", "window_size", "ArattnError", "lib", "lib_path",
     "rope_fwd", "rope_bwd", "flash_attn_fwd", "flash_attn_bwd_precompute_d", "flash_attn_bwd_dq",
-    "flash_attn_bwd_dkv", "AttnParams", "attn_fwd", "attn_bwd", "attention", "shard_units",
+    "flash_attn_bwd_dkv", "AttnParams", "attn_fwd", "attn_bwd", "attention", "check_device_status", "shard_units",
 ]

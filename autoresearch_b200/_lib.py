@@ -54,10 +54,13 @@ SIGNATURES = {
     "ar_version": (ctypes.c_int32, []),
     "ar_last_error": (ctypes.c_char_p, []),
     "ar_device_status": (ctypes.c_int32, []),
+    "ar_selftest_wait_timeout": (ctypes.c_int32, [ctypes.c_int32, _vp]),
     "ar_rope_fwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "ar_rope_bwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "ar_qk_norm_rope_cast": (ctypes.c_int32, [_vp] * 10 + [_i64] * 4 + [ctypes.c_float, _vp]),
     "ar_flash_attn_fwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "ar_flash_attn_fwd_noalloc": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "ar_noalloc_status": (ctypes.c_int32, []),
     "ar_flash_attn_bwd_precompute_d": (ctypes.c_int32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "ar_flash_attn_bwd_dq": (ctypes.c_int32, [_vp] * 7 + [_i64] * 5 + [_vp]),
     "ar_flash_attn_bwd_dkv": (ctypes.c_int32, [_vp] * 8 + [_i64] * 5 + [_vp]),

@@ -42,9 +42,11 @@ class AttnParams:
     k_rot: Optional[torch.Tensor] = None
 
 
-def _check(t: torch.Tensor, name: str, shape=None, dtype=None) -> int:
+def _check(t: torch.Tensor, name: str, shape=None, dtype=None, device=None) -> int:
     if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
         raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device} (all tensors of a call share one device)")
     if shape is not None and tuple(t.shape) != tuple(shape):
         raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
     if dtype is not None and t.dtype != dtype:
@@ -52,7 +54,33 @@ def _check(t: torch.Tensor, name: str, shape=None, dtype=None) -> int:
     return t.data_ptr()
 
 
+def _workspace(c: "_lib.ArAttnParams", which_pass: int, device) -> Optional[torch.Tensor]:
+    """Scratch for one call, taken from torch's stream-aware caching allocator (so that calls on
+    different streams never share it and nothing synchronises the device) and handed to the
+    library as caller workspace.  Returns the tensor, which the caller keeps alive until the call
+    has been enqueued (the allocator then defers its reuse to the stream it was allocated on)."""
+    need = int(_lib.lib().ar_attn_workspace_bytes(ctypes.byref(c), which_pass))
+    if need == 0 or c.stream != torch.cuda.current_stream(device).cuda_stream:
+        return None     # nothing needed, or a foreign stream: the library's own per-device scratch serves
+    buf = torch.empty(need + 1024, dtype=torch.uint8, device=device)
+    base = (buf.data_ptr() + 1023) // 1024 * 1024      # the library wants 1024-byte alignment
+    c.workspace = base
+    c.workspace_bytes = need
+    return buf
+
+
+def check_device_status(device=None) -> None:
+    """Per-step hook: waits for `device` (default: the current one) and raises ArattnError if any
+    attention kernel since the last check abandoned a bounded wait.  After such an event the
+    kernels of later calls return without writing their outputs until this check has been made,
+    so a training loop calls it once per step before it trusts the step's results."""
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _lib.check(_lib.lib().ar_device_status())
+
+
 def _c_params(p: AttnParams, q: torch.Tensor) -> _lib.ArAttnParams:
+    if not isinstance(q, torch.Tensor) or not q.is_cuda:
+        raise ValueError("q must be a CUDA tensor")
     if q.dim() != 4:
         raise ValueError("q must be [B, T, H, D]")
     if q.dtype not in _DT:
@@ -72,8 +100,8 @@ def _c_params(p: AttnParams, q: torch.Tensor) -> _lib.ArAttnParams:
     if p.rope is not None:
         cos, sin = p.rope
         c.rope_mode = 1
-        c.cos_buf = _check(cos, "cos", dtype=torch.float32)
-        c.sin_buf = _check(sin, "sin", dtype=torch.float32)
+        c.cos_buf = _check(cos, "cos", dtype=torch.float32, device=q.device)
+        c.sin_buf = _check(sin, "sin", dtype=torch.float32, device=q.device)
         if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != D // 2:
             raise ValueError("rope tables must both be [rows, D/2]")
         c.rope_rows = cos.shape[0]
@@ -84,43 +112,50 @@ def _c_params(p: AttnParams, q: torch.Tensor) -> _lib.ArAttnParams:
     if p.q_rot is not None:
         if p.rope is None:
             raise ValueError("q_rot / k_rot need rope tables")
-        c.q_rot = _check(p.q_rot, "q_rot", tuple(q.shape), torch.bfloat16)
-        c.k_rot = _check(p.k_rot, "k_rot", tuple(q.shape), torch.bfloat16)
+        c.q_rot = _check(p.q_rot, "q_rot", tuple(q.shape), torch.bfloat16, q.device)
+        c.k_rot = _check(p.k_rot, "k_rot", tuple(q.shape), torch.bfloat16, q.device)
     c.workspace = None
     c.workspace_bytes = 0
-    c.stream = p.stream if p.stream is not None else torch.cuda.current_stream().cuda_stream
+    c.stream = p.stream if p.stream is not None else torch.cuda.current_stream(q.device).cuda_stream
     return c
 
 
 def attn_fwd(q, k, v, params: AttnParams, out=None, lse=None):
     """Returns (o [B,T,H,D] in q's dtype, lse [B,T,H] fp32)."""
     c = _c_params(params, q)
-    shape = tuple(q.shape)
+    shape, dev = tuple(q.shape), q.device
     if out is None:
         out = torch.empty_like(q)
     if lse is None:
-        lse = torch.empty(shape[:3], dtype=torch.float32, device=q.device)
-    _lib.check(_lib.lib().ar_attn_fwd(ctypes.byref(c), _check(q, "q"), _check(k, "k", shape, q.dtype),
-                                      _check(v, "v", shape, q.dtype), _check(out, "out", shape, q.dtype),
-                                      _check(lse, "lse", shape[:3], torch.float32)))
+        lse = torch.empty(shape[:3], dtype=torch.float32, device=dev)
+    args = (_check(q, "q"), _check(k, "k", shape, q.dtype, dev), _check(v, "v", shape, q.dtype, dev),
+            _check(out, "out", shape, q.dtype, dev), _check(lse, "lse", shape[:3], torch.float32, dev))
+    # the library works on the CURRENT device (status word, launches): make it the tensors' device
+    with torch.cuda.device(dev):
+        ws = _workspace(c, 0, dev)
+        _lib.check(_lib.lib().ar_attn_fwd(ctypes.byref(c), *args))
+        del ws
     return out, lse
 
 
 def attn_bwd(q, k, v, o, d_o, lse, params: AttnParams, d_buf=None, dq=None, dk=None, dv=None):
     """Returns (dq, dk, dv, d_buf)."""
     c = _c_params(params, q)
-    shape = tuple(q.shape)
+    shape, dev = tuple(q.shape), q.device
     gd = params.grad_dtype
     if d_buf is None:
-        d_buf = torch.empty(shape[:3], dtype=torch.float32, device=q.device)
-    dq = torch.empty(shape, dtype=gd, device=q.device) if dq is None else dq
-    dk = torch.empty(shape, dtype=gd, device=q.device) if dk is None else dk
-    dv = torch.empty(shape, dtype=gd, device=q.device) if dv is None else dv
-    _lib.check(_lib.lib().ar_attn_bwd(
-        ctypes.byref(c), _check(q, "q"), _check(k, "k", shape, q.dtype), _check(v, "v", shape, q.dtype),
-        _check(o, "o", shape, q.dtype), _check(d_o, "d_o", shape, q.dtype),
-        _check(lse, "lse", shape[:3], torch.float32), _check(d_buf, "d_buf", shape[:3], torch.float32),
-        _check(dq, "dq", shape, gd), _check(dk, "dk", shape, gd), _check(dv, "dv", shape, gd)))
+        d_buf = torch.empty(shape[:3], dtype=torch.float32, device=dev)
+    dq = torch.empty(shape, dtype=gd, device=dev) if dq is None else dq
+    dk = torch.empty(shape, dtype=gd, device=dev) if dk is None else dk
+    dv = torch.empty(shape, dtype=gd, device=dev) if dv is None else dv
+    args = (_check(q, "q"), _check(k, "k", shape, q.dtype, dev), _check(v, "v", shape, q.dtype, dev),
+            _check(o, "o", shape, q.dtype, dev), _check(d_o, "d_o", shape, q.dtype, dev),
+            _check(lse, "lse", shape[:3], torch.float32, dev), _check(d_buf, "d_buf", shape[:3], torch.float32, dev),
+            _check(dq, "dq", shape, gd, dev), _check(dk, "dk", shape, gd, dev), _check(dv, "dv", shape, gd, dev))
+    with torch.cuda.device(dev):
+        ws = _workspace(c, 1, dev)
+        _lib.check(_lib.lib().ar_attn_bwd(ctypes.byref(c), *args))
+        del ws
     return dq, dk, dv, d_buf
 
 

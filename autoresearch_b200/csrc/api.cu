@@ -263,6 +263,27 @@ AR_API ar_status ar_rope_bwd(float* grad_in, const float* grad_out, const float*
                      kRopeBwd, stream);
 }
 
+AR_API ar_status ar_qk_norm_rope_cast(void* q_rot, void* k_rot, void* v_bf16, float* rms_q, float* rms_k,
+                                      const float* q, const float* k, const float* v, const float* cos_buf,
+                                      const float* sin_buf, int64_t num_tokens, int64_t num_heads,
+                                      int64_t head_dim, int64_t seq_len, float eps, void* stream) {
+  if (!q_rot || !k_rot || !q || !k || !cos_buf || !sin_buf) return fail(AR_ERR_BAD_ARG, "null pointer");
+  if ((v == nullptr) != (v_bf16 == nullptr)) return fail(AR_ERR_BAD_ARG, "v and v_bf16 must be given together");
+  if (num_tokens <= 0 || num_heads <= 0) return fail(AR_ERR_BAD_ARG, "num_tokens, num_heads must be positive");
+  if (head_dim != kHeadDim) return fail(AR_ERR_UNSUPPORTED, "head_dim %lld is not supported (only 128)", (long long)head_dim);
+  if (!(eps >= 0.f)) return fail(AR_ERR_BAD_ARG, "eps must be non-negative");
+  if (!aligned16(q_rot) || !aligned16(k_rot) || !aligned16(v_bf16) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
+      !aligned16(cos_buf) || !aligned16(sin_buf))
+    return fail(AR_ERR_BAD_ARG, "tensor pointers must be 16-byte aligned");
+  DeviceState* st;
+  AR_TRY(device_state(&st));
+  AR_CUDA(launch_qk_norm_rope_cast_128(static_cast<__nv_bfloat16*>(q_rot), static_cast<__nv_bfloat16*>(k_rot),
+                                       static_cast<__nv_bfloat16*>(v_bf16), rms_q, rms_k, q, k, v, cos_buf, sin_buf,
+                                       num_tokens * num_heads, (int)num_heads, seq_len, eps, (cudaStream_t)stream),
+          "qk_norm_rope_cast launch");
+  return AR_OK;
+}
+
 AR_API ar_status ar_flash_attn_fwd(float* output, float* lse_out, const float* q, const float* k,
                                    const float* v, int64_t B, int64_t T, int64_t num_heads,
                                    int64_t head_dim, int64_t window_size, void* stream) {
@@ -351,6 +372,56 @@ AR_API ar_status ar_flash_attn_fwd_noalloc(float* output, float* lse_out, const 
   view.status = na->status;
   return run_fwd(&view, qb, kb, vb, output, 1, lse_out, B, T, num_heads, norm_window(window_size, T),
                  nullptr, nullptr, s);
+}
+
+AR_API ar_status ar_noalloc_status(void) {
+  NoAllocState* na;
+  AR_TRY(noalloc_state(&na));
+  AR_CUDA(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+  uint32_t word = 0;
+  AR_CUDA(cudaMemcpy(&word, na->status, sizeof(word), cudaMemcpyDeviceToHost), "cudaMemcpy(noalloc status)");
+  if (word != 0) {
+    const uint32_t zero = 0;
+    AR_CUDA(cudaMemcpy(na->status, &zero, sizeof(zero), cudaMemcpyHostToDevice), "cudaMemcpy(clear noalloc status)");
+    return fail(AR_ERR_TIMEOUT, "a device-side bounded wait gave up in an allocation-free call (status word 0x%x)", word);
+  }
+  return AR_OK;
+}
+
+// ---- self-test of the time-out path ------------------------------------------------------------
+// One warp waits on an mbarrier that nothing ever arrives at, with a limit of about a millisecond
+// instead of the kernels' 0.2 s.  The wait runs out, flags the status word exactly as an abandoned
+// wait inside an attention kernel would, and the kernel returns normally.
+constexpr long long kSelfTestLimitCycles = 2000000ll;
+__global__ void __launch_bounds__(32, 1) selftest_wait_kernel(uint32_t* status) {
+  __shared__ alignas(8) uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  WaitCtx w{status, smem_u32(&abort_flag)};
+  (void)mbar_wait<0, kSelfTestLimitCycles>(w, smem_u32(&bar), 0);
+}
+
+AR_API ar_status ar_selftest_wait_timeout(int32_t which, void* stream) {
+  uint32_t* word = nullptr;
+  if (which == 0) {
+    DeviceState* st;
+    AR_TRY(device_state(&st));
+    word = st->status;
+  } else if (which == 1) {
+    NoAllocState* na;
+    AR_TRY(noalloc_state(&na));
+    word = na->status;
+  } else {
+    return fail(AR_ERR_BAD_ARG, "which must be 0 (ar_device_status word) or 1 (ar_noalloc_status word)");
+  }
+  selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(word);
+  AR_CUDA(cudaGetLastError(), "selftest launch");
+  return AR_OK;
 }
 
 AR_API ar_status ar_flash_attn_bwd_precompute_d(float* d_out, const float* output,

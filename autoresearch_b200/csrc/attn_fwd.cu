@@ -8,7 +8,9 @@
 //   warps 0-3   softmax of tile A (thread r = query row r: no shuffles needed for row
 //               statistics because tcgen05.ld 32x32b hands each thread a whole row)
 //   warps 4-7   softmax of tile B
-//   warps 8-11  (kRope only) rotate each K tile in shared memory after it lands
+//   warps 8-11  kRope: rotate each K tile in shared memory after it lands;
+//               otherwise: write-out of both tiles (O / l, LSE), so that the softmax warps go
+//               straight on to the next item
 //   warp  12    TMA producer: Q per item, K/V tiles through a 2-stage ring that runs on across items
 //   warps 13,14 tcgen05.mma issuers, one per Q tile (warp 13 owns the TMEM allocation)
 // Registers are moved from the data-movement warpgroups to the softmax warpgroups
@@ -19,26 +21,16 @@
 // P_X, rescale O_X  ->  O_X += P_X V_j (A operand from TMEM, V as MN-major B operand).
 // KV tiles outside the causal / sliding-window band of a Q tile are never visited; only
 // tiles crossed by a mask edge pay for element masking.
-// At the end of an item each softmax thread pulls its O row into registers (which frees the
-// accumulator for the next item), divides by the row sum and writes the rows out with plain
-// coalesced stores through a per-warp transposition buffer.
+// At the end of an item the O rows are divided by the row sum and written out with plain coalesced
+// stores through a per-warp transposition buffer.  Without rotate-on-load the otherwise idle
+// warpgroup 8-11 does that: the softmax threads leave their row statistics in shared memory and
+// start the next item at once, so the two tiles keep taking turns across item boundaries instead of
+// one tile running alone (at the latency of its S -> P -> PV chain) while the other writes out.
+// With rotate-on-load that warpgroup is busy and each softmax thread writes its own row out.
 #include "attn_common.cuh"
-
-// back-off (ns) of the TMA producer's polling; its wake-up latency is covered by the rings
-#ifndef AR_TMA_SLEEP
-#define AR_TMA_SLEEP 0
-#endif
 
 namespace ar {
 
-// P hand-over arrivals: every softmax thread arrives (measured 8 % faster for the whole kernel than
-// one elected lane per warp behind a __syncwarp)
-#ifndef AR_FWD_ELECT
-#define AR_FWD_ELECT 0
-#endif
-#ifndef AR_TRACE_BX
-#define AR_TRACE_BX 0
-#endif
 constexpr int kFwdStages = 2;
 constexpr int kFwdThreads = 512;  // four warpgroups (see the role list above)
 constexpr int kWarpRot0 = 8;      // warps 8-11: K rotation (idle without rotate-on-load)
@@ -58,6 +50,7 @@ struct FwdSmem {
   uint64_t k_full[kFwdStages], k_rot[kFwdStages], k_empty[kFwdStages];
   uint64_t v_full[kFwdStages], v_empty[kFwdStages];
   uint64_t s_full[2], p_ready[2][2], o_final[2], o_free[2];   // p_ready: one per 64-key half of P
+  uint64_t stat_ready[2];   // the tile's row statistics of this item are in shared memory (write-out warps)
   uint32_t exp_cnt[2];   // per tile: exponential phases finished so far x 4 warps (monotonic)
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -104,7 +97,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   grid_dep_launch_dependents();   // all CTAs of this grid are resident: the next kernel may be scheduled
   WaitCtx w{p.status, smem_u32(&sm.abort_flag)};
 #ifdef AR_TRACE
-  const bool trace_on = blockIdx.x == AR_TRACE_BX && lane == 0 && (warp == 0 || warp == 4 || warp == 13 || warp == 14);
+  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 13 || warp == 14);
 #endif
 
   if (threadIdx.x == 0) {
@@ -113,10 +106,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int X = 0; X < 2; ++X) {
       mbar_init(smem_u32(&sm.q_ready[X]), 128);
       mbar_init(smem_u32(&sm.s_full[X]), 1);
-      mbar_init(smem_u32(&sm.p_ready[X][0]), AR_FWD_ELECT ? 4 : 128);   // one arrival per softmax warp
-      mbar_init(smem_u32(&sm.p_ready[X][1]), AR_FWD_ELECT ? 4 : 128);
+      // every softmax thread arrives (measured 8 % faster for the whole kernel than one elected
+      // lane per warp behind a __syncwarp)
+      mbar_init(smem_u32(&sm.p_ready[X][0]), 128);
+      mbar_init(smem_u32(&sm.p_ready[X][1]), 128);
       mbar_init(smem_u32(&sm.o_final[X]), 1);
-      mbar_init(smem_u32(&sm.o_free[X]), 4);       // the tile's O rows are in registers
+      mbar_init(smem_u32(&sm.o_free[X]), 4);       // the tile's O rows have left tensor memory
+      mbar_init(smem_u32(&sm.stat_ready[X]), 4);
     }
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(smem_u32(&sm.k_full[s]), 1);
@@ -145,7 +141,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (warp < 8) {
     // ------------------------------------------------------------------ softmax warps
-    setmaxnreg_inc<200>();
+    if (kRope) setmaxnreg_inc<200>(); else setmaxnreg_inc<192>();   // without rotate-on-load the write-out warps take the difference
     const int X = warp >> 2;
     const int r = threadIdx.x & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -305,12 +301,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           tmem_wait_st();
           tc_fence_before();
-          if (AR_FWD_ELECT) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready + 8 * c);
-          } else {
-            mbar_arrive(p_ready + 8 * c);
-          }
+          mbar_arrive(p_ready + 8 * c);
           TRACE(X, g_own + it, 5 + 2 * c);
         }
         float sum0, sum1;
@@ -320,6 +311,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (!ok) break;
       TRACE(X, 56 + (n & 3), 1);
 
+      if (!kRope) {
+        // Hand the row statistics to the write-out warps.  They live in the transposition buffers
+        // of softmax warps 4-7, unused in this mode: [tile][l | m][row].  The previous item's
+        // statistics have been read once o_free has completed its phase (long ago: the first P V of
+        // this item waited for the same phase).
+        if (nx > 0 && !mbar_wait(w, smem_u32(&sm.o_free[X]), (nx - 1) & 1)) { ok = false; break; }
+        float* stat = reinterpret_cast<float*>(sm.epi[4]) + X * 256;
+        stat[r] = l_run;
+        stat[128 + r] = m_ref;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.stat_ready[X]));
+        g_own += n_it;
+        g_oth += n_other;
+        ++nx;
+        ++n;
+        continue;
+      }
       // epilogue: O / l and LSE = m * scale + ln(l)   (ops.mojo:316-321)
       if (!mbar_wait(w, smem_u32(&sm.o_final[X]), nx & 1)) { ok = false; break; }
       tc_fence_after();
@@ -390,7 +398,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (item == -2) continue;
         const FwdItem wi = fwd_item(item, p.dims, n_qb);
         // Q may be replaced once the previous item's last S products have completed
-        if (n > 0 && !mbar_wait<AR_TMA_SLEEP>(w, smem_u32(&sm.q_free), (n - 1) & 1)) break;
+        if (n > 0 && !mbar_wait(w, smem_u32(&sm.q_free), (n - 1) & 1)) break;
         if (lane == 0) {
           mbar_arrive_expect_tx(smem_u32(&sm.q_full), 2 * kTileBytes);
 #pragma unroll
@@ -402,13 +410,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int j = wi.jlo; j <= wi.jhi; ++j, ++g) {
           const int s = g % kFwdStages;
           const uint32_t par = ((g / kFwdStages) & 1) ^ 1;
-          if (!mbar_wait<AR_TMA_SLEEP>(w, smem_u32(&sm.k_empty[s]), par)) { ok = false; break; }
+          if (!mbar_wait(w, smem_u32(&sm.k_empty[s]), par)) { ok = false; break; }
           if (lane == 0) {
             mbar_arrive_expect_tx(smem_u32(&sm.k_full[s]), kTileBytes);
             tma_load_4d(smem_u32(sm.k[s]), &map_k, smem_u32(&sm.k_full[s]), 0, wi.h, j * kTile, wi.b);
             tma_load_4d(smem_u32(sm.k[s]) + kHalfBytes, &map_k, smem_u32(&sm.k_full[s]), 64, wi.h, j * kTile, wi.b);
           }
-          if (!mbar_wait<AR_TMA_SLEEP>(w, smem_u32(&sm.v_empty[s]), par)) { ok = false; break; }
+          if (!mbar_wait(w, smem_u32(&sm.v_empty[s]), par)) { ok = false; break; }
           if (lane == 0) {
             mbar_arrive_expect_tx(smem_u32(&sm.v_full[s]), kTileBytes);
             tma_load_4d(smem_u32(sm.v[s]), &map_v, smem_u32(&sm.v_full[s]), 0, wi.h, j * kTile, wi.b);
@@ -541,10 +549,86 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
     }
   } else {
-    // ------------------------------------------------------------------ K rotation warps
-    setmaxnreg_dec<56>();
+    // ------------------------------------------------------------------ K rotation / write-out warps
+    if (kRope) setmaxnreg_dec<56>(); else setmaxnreg_dec<72>();
     const int r = threadIdx.x - kWarpRot0 * 32;
-    if (kRope) {
+    if (!kRope) {
+      // ------------------------------------------------------------------ write-out warps
+      // Thread r takes row r of tile A, then of tile B: O / l as bf16 or fp32 and
+      // LSE = m * scale + ln(l) (ops.mojo:316-321).  O is read 32 columns at a time and leaves
+      // through this warp's transposition buffer; the accumulator is released to the next item as
+      // soon as its last columns are in registers.
+      const int wq = warp - kWarpRot0;
+      const uint32_t lane_off = static_cast<uint32_t>(wq * 32) << 16;
+      const uint32_t epi = smem_u32(sm.epi[wq]);
+      const uint32_t wbase = epi + lane * 128u, sw = lane & 7u;
+      int nxe[2] = {0, 0};
+      bool ok = true;
+      for (int kk = 0; ok; ++kk) {
+        const int item = sched_item(kk, n_items);
+        if (item == -1) break;
+        if (item == -2) continue;
+        const FwdItem wi = fwd_item(item, p.dims, n_qb);
+#pragma unroll
+        for (int X = 0; X < 2; ++X) {
+          if (!(X == 0 ? wi.act[0] : wi.act[1])) continue;
+          const int ph = (X == 0 ? nxe[0] : nxe[1]) & 1;
+          if (!mbar_wait(w, smem_u32(&sm.stat_ready[X]), ph)) { ok = false; break; }
+          const float* stat = reinterpret_cast<const float*>(sm.epi[4]) + X * 256;
+          const float l_row = stat[r] * kTruncGainInv;   // the row sum was accumulated from the inflated P
+          const float m_row = stat[128 + r];
+          if (!mbar_wait(w, smem_u32(&sm.o_final[X]), ph)) { ok = false; break; }
+          tc_fence_after();
+          const float inv_l = 1.f / l_row;
+          const uint32_t tO = tmem + 256 + X * 128 + lane_off;
+          const int qlo = wi.q0 + kTile * X, qrow = qlo + r;
+          const int esize = p.o_f32 ? 4 : 2;
+          const size_t row_stride = (size_t)p.dims.H * 128 * esize;
+          const int wrow0 = qlo + 32 * wq;   // first row of this warp's 32-row block
+          uint8_t* gout = static_cast<uint8_t*>(p.o) + (((size_t)wi.b * T + wrow0) * p.dims.H + wi.h) * 128 * esize;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t og[32];
+            tmem_ld32_wait(tO + c * 32, og);
+            if (c == 3) {   // the next item may overwrite O_X
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&sm.o_free[X]));
+            }
+            if (p.o_f32) {
+#pragma unroll
+              for (uint32_t j = 0; j < 8; ++j)
+                sts128(wbase + ((j ^ sw) << 4),
+                       make_uint4(__float_as_uint(__uint_as_float(og[4 * j]) * inv_l),
+                                  __float_as_uint(__uint_as_float(og[4 * j + 1]) * inv_l),
+                                  __float_as_uint(__uint_as_float(og[4 * j + 2]) * inv_l),
+                                  __float_as_uint(__uint_as_float(og[4 * j + 3]) * inv_l)));
+              __syncwarp();
+              store_staged_rows<8>(epi, 0, lane, 0, gout + c * 128, row_stride, T - wrow0);
+              __syncwarp();
+            } else {
+              // two 32-column chunks make one 128-byte block of bf16
+#pragma unroll
+              for (uint32_t j = 0; j < 4; ++j) {
+                const int o = 8 * j;
+                sts128(wbase + (((j + 4 * (c & 1)) ^ sw) << 4),
+                       make_uint4(pack_bf16x2(__uint_as_float(og[o]) * inv_l, __uint_as_float(og[o + 1]) * inv_l),
+                                  pack_bf16x2(__uint_as_float(og[o + 2]) * inv_l, __uint_as_float(og[o + 3]) * inv_l),
+                                  pack_bf16x2(__uint_as_float(og[o + 4]) * inv_l, __uint_as_float(og[o + 5]) * inv_l),
+                                  pack_bf16x2(__uint_as_float(og[o + 6]) * inv_l, __uint_as_float(og[o + 7]) * inv_l)));
+              }
+              if (c & 1) {
+                __syncwarp();
+                store_staged_rows<8>(epi, 0, lane, 0, gout + (c >> 1) * 128, row_stride, T - wrow0);
+                __syncwarp();
+              }
+            }
+          }
+          if (qrow < T) p.lse[((size_t)wi.b * T + qrow) * p.dims.H + wi.h] = m_row * p.scale + logf(l_row);
+          if (X == 0) ++nxe[0]; else ++nxe[1];
+        }
+      }
+    } else {
       int g = 0;
       bool ok = true;
       for (int kk = 0; ok; ++kk) {

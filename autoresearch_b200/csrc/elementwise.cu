@@ -108,6 +108,84 @@ rope_pair_bf16_128_kernel(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bf
   }
 }
 
+// Prologue of the attention path in one launch: the reference's rope_fwd on q and k followed by its
+// per-head rmsnorm_fwd on q and k (model.mojo:668-687; ops.mojo:209-238, 61-104), with the result
+// cast to the bf16 operands the tensor-core kernels read, and v cast alongside (blockIdx.y picks
+// q, k or v).  One thread owns 8 consecutive d of the first half of a (token, head) row and the
+// matching 8 of the second half - the two halves a rotation pairs - so the rotation is local to
+// the thread; the sum of squares of a row meets across its 8 threads by shuffles.  As in the
+// reference the row is rotated first and normalised by sqrt(mean(y^2) + eps) of the ROTATED row
+// (a rotation keeps the sum of squares, so this differs from normalising first only by rounding).
+// rms_q / rms_k (optional) receive that square root per row, as rmsnorm_fwd's rms_out does.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cast_128_kernel(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* rms_q,
+                             float* rms_k, const float* __restrict__ q, const float* __restrict__ k,
+                             const float* __restrict__ v, const float* __restrict__ cos_buf,
+                             const float* __restrict__ sin_buf, long long rows, int num_heads, long long seq_len,
+                             float eps) {
+  const int which = blockIdx.y;   // 0: q, 1: k, 2: v
+  const float* in = which == 0 ? q : (which == 1 ? k : v);
+  __nv_bfloat16* out = which == 0 ? q_out : (which == 1 ? k_out : v_out);
+  float* rms_out = which == 0 ? rms_q : (which == 1 ? rms_k : nullptr);
+  const long long total = rows * 8;   // a multiple of 8: the 8 threads of a row always run together
+  for (long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x; tid < total;
+       tid += (long long)gridDim.x * blockDim.x) {
+    const long long row = tid >> 3;
+    const int g = static_cast<int>(tid & 7);
+    const long long base = row * 128 + g * 8;
+    const float4 a0 = *reinterpret_cast<const float4*>(in + base), a1 = *reinterpret_cast<const float4*>(in + base + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(in + base + 64), b1 = *reinterpret_cast<const float4*>(in + base + 68);
+    float x1[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    float x2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    if (which < 2) {
+      const long long token = row / num_heads;
+      const long long pos = seq_len > 0 ? token % seq_len : token;
+      const float4 c0 = __ldg(reinterpret_cast<const float4*>(cos_buf + pos * 64 + g * 8));
+      const float4 c1 = __ldg(reinterpret_cast<const float4*>(cos_buf + pos * 64 + g * 8 + 4));
+      const float4 s0 = __ldg(reinterpret_cast<const float4*>(sin_buf + pos * 64 + g * 8));
+      const float4 s1 = __ldg(reinterpret_cast<const float4*>(sin_buf + pos * 64 + g * 8 + 4));
+      const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float y1 = x1[i] * cs[i] + x2[i] * sn[i];    // ops.mojo:237-238
+        const float y2 = x2[i] * cs[i] - x1[i] * sn[i];
+        x1[i] = y1;
+        x2[i] = y2;
+        ss += y1 * y1 + y2 * y2;
+      }
+      // the 8 threads of a row are 8 consecutive lanes of one warp
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      const float rms = sqrtf(ss * (1.0f / 128.0f) + eps);  // ops.mojo:96-97
+      if (rms_out != nullptr && g == 0) rms_out[row] = rms;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x1[i] = x1[i] / rms;                                 // ops.mojo:101-102 divides
+        x2[i] = x2[i] / rms;
+      }
+    }
+    *reinterpret_cast<uint4*>(out + base) = make_uint4(pack_bf16x2(x1[0], x1[1]), pack_bf16x2(x1[2], x1[3]),
+                                                       pack_bf16x2(x1[4], x1[5]), pack_bf16x2(x1[6], x1[7]));
+    *reinterpret_cast<uint4*>(out + base + 64) = make_uint4(pack_bf16x2(x2[0], x2[1]), pack_bf16x2(x2[2], x2[3]),
+                                                            pack_bf16x2(x2[4], x2[5]), pack_bf16x2(x2[6], x2[7]));
+  }
+}
+
+cudaError_t launch_qk_norm_rope_cast_128(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* rms_q,
+                                         float* rms_k, const float* q, const float* k, const float* v,
+                                         const float* cos_buf, const float* sin_buf, long long rows, int num_heads,
+                                         long long seq_len, float eps, cudaStream_t stream) {
+  long long blocks = (rows * 8 + 255) / 256;
+  const long long cap = 148LL * 16;   // grid-stride beyond 16 blocks (of 256 threads) per SM
+  dim3 grid(static_cast<unsigned>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks)), v != nullptr ? 3 : 2);
+  qk_norm_rope_cast_128_kernel<<<grid, 256, 0, stream>>>(q_out, k_out, v_out, rms_q, rms_k, q, k, v, cos_buf, sin_buf,
+                                                         rows, num_heads, seq_len, eps);
+  return cudaGetLastError();
+}
+
 // Scalar form for head dims whose half is not a multiple of 4 (fp32 only; the rope mirrors).
 __global__ void __launch_bounds__(256)
 rope_scalar_kernel(float* out, const float* in,

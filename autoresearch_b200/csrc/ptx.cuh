@@ -62,11 +62,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-#ifdef AR_WAIT_TEST
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -75,11 +71,11 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false (to every lane of the warp alike) if the phase did
-// not complete within kWaitLimitCycles or another thread of the CTA already gave up;
+// not complete within kLimit cycles or another thread of the CTA already gave up;
 // in that case the status word is flagged and the caller must fall through to the
 // kernel's teardown.  Must be called by all 32 lanes of a warp together.  kSleepNs > 0 backs the
 // polling off (for waiters whose wake-up latency does not matter).
-template <int kSleepNs = 0>
+template <int kSleepNs = 0, long long kLimit = kWaitLimitCycles>
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32_t parity) {
   uint32_t ok = mbar_try_wait(bar, parity);
   if (!__all_sync(0xffffffffu, ok)) {
@@ -90,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait(const WaitCtx& w, uint32_t bar, uint32
       ok = mbar_try_wait(bar, parity);
       if (__all_sync(0xffffffffu, ok)) break;
       if ((++spins & 63u) == 0u) {
-        bool give_up = ld_shared_u32(w.abort_smem) != 0u || (clock64() - t0) > kWaitLimitCycles;
+        bool give_up = ld_shared_u32(w.abort_smem) != 0u || (clock64() - t0) > kLimit;
         if (__any_sync(0xffffffffu, give_up)) {
           if (lane_id() == 0) {
             st_shared_u32(w.abort_smem, 1u);

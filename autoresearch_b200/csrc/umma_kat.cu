@@ -147,398 +147,3 @@ extern "C" __attribute__((visibility("default"))) int32_t ar_kat_umma(const void
       ma, mb, (const __nv_bfloat16*)a, out, a_mode, b_mode, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
-
-namespace ar {
-
-// Throughput probe: every CTA issues `iters` back-to-back 128 x N x 128 products
-// (8 MMAs of K=16 each) into one accumulator and reports the cycles from the first
-// issue to the completion of the last.  mode 0: A and B from shared memory (K-major);
-// mode 1: A from tensor memory, B from shared memory (MN-major).  n_cols: 128 or 256.
-__global__ void __launch_bounds__(128, 1)
-kat_mma_rate_kernel(int mode, int n_cols, int iters, int style, unsigned long long* cycles,
-                    uint32_t* status) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint8_t* a = base;                  // 32 KB
-  uint8_t* b = base + 32768;          // up to 64 KB
-  uint64_t* bar = reinterpret_cast<uint64_t*>(base + 32768 + 65536);
-  uint32_t* misc = reinterpret_cast<uint32_t*>(bar + 1);
-  for (int i = threadIdx.x; i < (32768 + 65536) / 4; i += blockDim.x)
-    reinterpret_cast<uint32_t*>(base)[i] = 0x3c003c00u;  // small finite bf16 values
-  const uint32_t warp = threadIdx.x >> 5;
-  WaitCtx wctx{status, smem_u32(&misc[1])};
-  if (threadIdx.x == 0) {
-    mbar_init(smem_u32(bar), 1);
-    misc[1] = 0;
-    fence_mbar_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(&misc[0]), 512);
-    tmem_relinquish();
-  }
-  fence_proxy_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = misc[0];
-  long long t0 = 0;
-  // style 0: thread 0 issues; style 1: elected lane issues; style 2: warps 0 and 1 each issue
-  // their own stream into separate accumulators (columns [0,N) and [N,2N), N = 128 only).
-  const uint32_t n_issuers = (style == 2) ? 2u : 1u;
-  uint64_t* bar2 = bar + 2;
-  if (threadIdx.x == 0 && style == 2) {
-    mbar_init(smem_u32(bar2), 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  if (warp < n_issuers) {
-    const uint32_t idesc = make_idesc_bf16(128, n_cols, 0, mode == 1 ? 1u : 0u);
-    const uint32_t a_base = smem_u32(a), b_base = smem_u32(b);
-    const uint32_t acc = tmem + warp * 128;
-    const uint32_t mybar = smem_u32(warp == 0 ? bar : bar2);
-    t0 = clock64();
-    const bool issuer = (style == 1) ? elect_one() : ((threadIdx.x & 31) == 0);
-    if (style == 5) {
-      // convergent loop, leader chosen once, descriptors advanced by adding to a base
-      const uint32_t leader = ((threadIdx.x & 31) == 0) ? 1u : 0u;
-      const uint64_t a0 = make_sdesc_sw128(a_base, 0, 1024);
-      const uint64_t b0 = (mode == 0) ? make_sdesc_sw128(b_base, 0, 1024) : make_sdesc_sw128(b_base, 16384, 1024);
-      const uint32_t half_b = (n_cols * 128) >> 4;
-      for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          if (mode == 0) {
-            umma_ss_pred(leader, acc, a0 + (ks >> 2) * 1024 + (ks & 3) * 2, b0 + (ks >> 2) * half_b + (ks & 3) * 2,
-                         idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          } else {
-            umma_ts_pred(leader, acc, tmem + 256 + ks * 8, b0 + ks * 128, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          }
-        }
-      }
-      umma_commit_pred(leader, mybar);
-    } else if (style == 4) {
-      // warp-convergent issue: all lanes run the loop, elect.sync predicates inside the asm
-      for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          if (mode == 0) {
-            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma_ss_elect(acc, make_sdesc_sw128(a_base + off, 0, 1024),
-                          make_sdesc_sw128(b_base + (ks >> 2) * (n_cols * 128) + (ks & 3) * 32, 0, 1024), idesc,
-                          (it > 0 || ks > 0) ? 1u : 0u);
-          } else {
-            umma_ts_elect(acc, tmem + 256 + ks * 8, make_sdesc_sw128(b_base + ks * 2048, 16384, 1024), idesc,
-                          (it > 0 || ks > 0) ? 1u : 0u);
-          }
-        }
-      }
-      umma_commit_elect(mybar);
-    } else if (issuer && style == 3) {
-      // one thread, two independent accumulators, k-steps interleaved (N = 128)
-      for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            if (mode == 0) {
-              const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-              umma_ss(tmem + g * 128, make_sdesc_sw128(a_base + off, 0, 1024),
-                      make_sdesc_sw128(b_base + (ks >> 2) * (n_cols * 128) + (ks & 3) * 32, 0, 1024), idesc,
-                      (it > 0 || ks > 0) ? 1u : 0u);
-            } else {
-              umma_ts(tmem + g * 128, tmem + 256 + ks * 8, make_sdesc_sw128(b_base + ks * 2048, 16384, 1024),
-                      idesc, (it > 0 || ks > 0) ? 1u : 0u);
-            }
-          }
-        }
-      }
-      umma_commit(mybar);
-    } else if (issuer) {
-      for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          if (mode == 0) {
-            const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma_ss(acc, make_sdesc_sw128(a_base + off, 0, 1024),
-                    make_sdesc_sw128(b_base + (ks >> 2) * (n_cols * 128) + (ks & 3) * 32, 0, 1024), idesc,
-                    (it > 0 || ks > 0) ? 1u : 0u);
-          } else {
-            umma_ts(acc, tmem + 256 + ks * 8, make_sdesc_sw128(b_base + ks * 2048, 16384, 1024), idesc,
-                    (it > 0 || ks > 0) ? 1u : 0u);
-          }
-        }
-      }
-      umma_commit(mybar);
-    }
-    __syncwarp();
-    const long long t_issue = clock64();
-    const bool ok = mbar_wait(wctx, mybar, 0);
-    const long long t1 = clock64();
-    if ((threadIdx.x & 31) == 0 && ok && warp == 0) {
-      cycles[2 * blockIdx.x] = (unsigned long long)(t1 - t0);
-      cycles[2 * blockIdx.x + 1] = (unsigned long long)(t_issue - t0);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-}
-
-}  // namespace ar
-
-extern "C" __attribute__((visibility("default"))) int32_t ar_kat_mma_rate(int32_t mode, int32_t n_cols,
-                                                                          int32_t iters, int32_t style,
-                                                                          int32_t ctas,
-                                                                          unsigned long long* cycles,
-                                                                          uint32_t* status, void* stream) {
-  size_t smem = 32768 + 65536 + 64 + 1024;
-  if (cudaFuncSetAttribute(ar::kat_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem) != cudaSuccess)
-    return -3;
-  ar::kat_mma_rate_kernel<<<ctas, 128, smem, (cudaStream_t)stream>>>(mode, n_cols, iters, style, cycles,
-                                                                     status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
-}
-
-namespace ar {
-
-// Arithmetic-rate probe for the element-wise stage of the attention kernels: 256 threads per CTA
-// (two warps per scheduler), each repeatedly turns 64 register-resident scores into 32 packed
-// bf16x2 words.  mode 0: ex2 only; 1: fma + ex2; 2: fma + ex2 + sub + mul + cvt pack;
-// 3: same with the integer-pipe pack; 4: fma + sub + mul + integer pack, no ex2.
-template <int mode, int kUnroll = 1>
-__global__ void __launch_bounds__(256, 1)
-kat_math_rate_kernel(int iters, float c, float lse, float d, unsigned long long* cycles,
-                     uint32_t* sink) {
-  float s[64], g[64];
-#pragma unroll
-  for (int i = 0; i < 64; ++i) {
-    // lse doubles as a spread control: scores span about [-lse*30, lse*30] around 0
-    s[i] = lse * (float)(((i * 37 + threadIdx.x * 11) % 61) - 30);
-    g[i] = 0.5f + 0.001f * (float)i;
-  }
-  uint32_t acc = 0;
-  __syncthreads();
-  // d < 0 staggers the warps (each starts |d| * 40 * warp cycles later) so that the two warps of
-  // a scheduler run through different parts of the unrolled body at any time
-  if (d < 0.f) {
-    const long long until = clock64() + (long long)(-d * 40.f) * (threadIdx.x >> 5);
-    while (clock64() < until) {}
-  }
-  const long long t0 = clock64();
-#pragma unroll kUnroll
-  for (int it = 0; it < iters; ++it) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float x0 = s[2 * i], x1 = s[2 * i + 1];
-      if (mode != 0) { x0 = fmaf(x0, c, -lse); x1 = fmaf(x1, c, -lse); }
-      float p0 = x0, p1 = x1;
-      if (mode != 4) { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
-      uint32_t w;
-      if (mode >= 2) {
-        const float a0 = p0 * (g[2 * i] - d), a1 = p1 * (g[2 * i + 1] - d);
-        w = (mode == 2) ? pack_bf16x2(a0, a1) : pack_bf16x2_alu(a0, a1);
-      } else {
-        w = __float_as_uint(p0) ^ __float_as_uint(p1);
-      }
-      acc ^= w;
-      s[2 * i] += 1e-3f;   // keep iterations dependent on new inputs
-    }
-  }
-  const long long t1 = clock64();
-  if (threadIdx.x == 0) cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
-  if (acc == 0x12345678u) sink[0] = acc;
-}
-
-}  // namespace ar
-
-extern "C" __attribute__((visibility("default"))) int32_t ar_kat_math_rate(int32_t mode, int32_t iters,
-                                                                           unsigned long long* cycles,
-                                                                           uint32_t* sink, void* stream) {
-  cudaStream_t s = (cudaStream_t)stream;
-  if (mode >= 50 && mode < 60) {   // staggered warps, body unrolled 8x (mode 50) or 1x (mode 51)
-    if (mode == 50) ar::kat_math_rate_kernel<3, 8><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, -7.f, cycles, sink);
-    else ar::kat_math_rate_kernel<3, 1><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, -7.f, cycles, sink);
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
-  }
-  if (mode >= 100) {   // value-range variants of the full loop: spread = (mode - 100) / 10
-    ar::kat_math_rate_kernel<3><<<148, 256, 0, s>>>(iters, 0.1275f, (float)(mode - 100) * 0.1f, 0.25f, cycles, sink);
-    return cudaGetLastError() == cudaSuccess ? 0 : -3;
-  }
-  switch (mode) {
-    case 0: ar::kat_math_rate_kernel<0><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 1: ar::kat_math_rate_kernel<1><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 2: ar::kat_math_rate_kernel<2><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 3: ar::kat_math_rate_kernel<3><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 4: ar::kat_math_rate_kernel<4><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 5: ar::kat_math_rate_kernel<3, 4><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    case 6: ar::kat_math_rate_kernel<3, 8><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-    default: ar::kat_math_rate_kernel<3, 20><<<148, 256, 0, s>>>(iters, 0.1275f, 3.0f, 0.25f, cycles, sink); break;
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
-}
-
-namespace ar {
-
-// Interference probe: warps 0-7 run the element-wise math of the dQ kernel (fma, ex2, sub, mul,
-// pack) from registers while, if with_mma != 0, warp 8 keeps the tensor pipe busy with
-// back-to-back 128x128x128 SS products.  Reports the math time per 64 elements per thread.
-__global__ void __launch_bounds__(512, 1)
-kat_math_vs_mma_kernel(int with_mma, int iters, float c, float lse, float d, unsigned long long* cycles,
-                       uint32_t* sink, uint32_t* status) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint64_t* bar = reinterpret_cast<uint64_t*>(base + 65536);
-  uint32_t* misc = reinterpret_cast<uint32_t*>(bar + 4);
-  volatile uint32_t* stop = misc + 2;
-  for (int i = threadIdx.x; i < 65536 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(base)[i] = 0x3c003c00u;
-  const uint32_t warp = threadIdx.x >> 5;
-  WaitCtx wctx{status, smem_u32(&misc[1])};
-  if (threadIdx.x == 0) {
-    mbar_init(smem_u32(bar), 1);
-    mbar_init(smem_u32(bar + 1), 1);
-    mbar_init(smem_u32(bar + 2), 1);
-    mbar_init(smem_u32(bar + 3), 1);
-    misc[1] = 0;
-    misc[2] = 0;
-    misc[3] = 0;
-    fence_mbar_init();
-  }
-  if (warp == 8) {
-    tmem_alloc(smem_u32(&misc[0]), 512);
-    tmem_relinquish();
-  }
-  fence_proxy_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = misc[0];
-  const int n_spin = with_mma / 10;   // tens digit: warps that poll an mbarrier until the math is done
-  with_mma %= 10;
-  if (warp >= 11) {
-    if ((int)warp - 11 < n_spin) {
-      int polls = 0;
-      while (*stop == 0u && polls < 20000000) {   // bounded
-        if (mbar_try_wait(smem_u32(bar + 3), 0)) break;
-        ++polls;
-      }
-    }
-  } else if (warp >= 8) {
-    // with_mma = number of issuing warps (0-3), each with its own accumulator pair
-    if ((int)warp - 8 < with_mma) {
-      const uint32_t idesc = make_idesc_bf16(128, 128, 0, 0);
-      const uint32_t a_base = smem_u32(base), b_base = smem_u32(base + 32768);
-      int n = 0;
-      while (*stop == 0u && n < 100000) {   // bounded
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          umma_ss_elect(tmem + (warp - 8) * 128, make_sdesc_sw128(a_base + off, 0, 1024),
-                        make_sdesc_sw128(b_base + off, 0, 1024), idesc, ks > 0);
-        }
-        ++n;
-      }
-      umma_commit_elect(smem_u32(bar + (warp - 8)));
-      mbar_wait(wctx, smem_u32(bar + (warp - 8)), 0);
-    }
-  } else {
-    float s[64], g[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      s[i] = -0.01f * (float)(i + threadIdx.x % 7);
-      g[i] = 0.5f + 0.001f * (float)i;
-    }
-    uint32_t acc = 0;
-    const long long t0 = clock64();
-    if (iters < 0) {
-      // tensor-memory round trips instead of arithmetic: load 32 columns of an accumulator no
-      // MMA is writing (columns 384..415), wait, repeat
-      const uint32_t lane_addr = tmem + 384 + (((warp & 3) * 32u) << 16);
-      for (int it = 0; it < -iters; ++it) {
-        uint32_t rg[32];
-        tmem_ld32_wait(lane_addr, rg);
-        acc ^= rg[it & 31];
-      }
-    }
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = ex2_approx(fmaf(s[2 * i], c, -lse)), p1 = ex2_approx(fmaf(s[2 * i + 1], c, -lse));
-        acc ^= pack_bf16x2_alu(p0 * (g[2 * i] - d), p1 * (g[2 * i + 1] - d));
-        s[2 * i] += 1e-3f;
-      }
-    }
-    const long long t1 = clock64();
-    if (threadIdx.x == 0) cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
-    if (acc == 0x12345678u) sink[0] = acc;
-    // every math warp passes here; the last arrival releases the MMA warp
-    __threadfence_block();
-    if ((threadIdx.x & 31) == 0 && atomicAdd(misc + 3, 1u) == 7u) *stop = 1u;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem, 512);
-}
-
-}  // namespace ar
-
-extern "C" __attribute__((visibility("default"))) int32_t ar_kat_math_vs_mma(int32_t with_mma, int32_t iters,
-                                                                             unsigned long long* cycles,
-                                                                             uint32_t* sink, uint32_t* status,
-                                                                             void* stream) {
-  size_t smem = 65536 + 128 + 1024;
-  if (cudaFuncSetAttribute(ar::kat_math_vs_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
-    return -3;
-  ar::kat_math_vs_mma_kernel<<<148, 512, smem, (cudaStream_t)stream>>>(with_mma, iters, 0.1275f, 3.0f, 0.25f,
-                                                                        cycles, sink, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
-}
-
-namespace ar {
-
-// Does warpgroup register re-allocation change arithmetic throughput?  512 threads; warps 0-7 run
-// the element-wise loop; with `realloc` they first grow to 200 registers while warps 8-15 shrink
-// to 56 (the pattern of the attention kernels), otherwise nothing is re-allocated.
-__global__ void __launch_bounds__(512, 1)
-kat_math_setmaxnreg_kernel(int realloc, int iters, float c, float lse, float d, unsigned long long* cycles,
-                           uint32_t* sink) {
-  const uint32_t warp = threadIdx.x >> 5;
-  if (warp >= 8) {
-    if (realloc) setmaxnreg_dec<56>();
-  } else {
-    if (realloc) setmaxnreg_inc<200>();
-    float s[64], g[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      s[i] = lse * (float)(((i * 37 + threadIdx.x * 11) % 61) - 30);
-      g[i] = 0.5f + 0.001f * (float)i;
-    }
-    uint32_t acc = 0;
-    const long long t0 = clock64();
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = ex2_approx(fmaf(s[2 * i], c, -lse)), p1 = ex2_approx(fmaf(s[2 * i + 1], c, -lse));
-        acc ^= pack_bf16x2_alu(p0 * (g[2 * i] - d), p1 * (g[2 * i + 1] - d));
-        s[2 * i] += 1e-3f;
-      }
-    }
-    const long long t1 = clock64();
-    if (threadIdx.x == 0) cycles[blockIdx.x] = (unsigned long long)(t1 - t0);
-    if (acc == 0x12345678u) sink[0] = acc;
-  }
-  __syncthreads();
-}
-
-}  // namespace ar
-
-extern "C" __attribute__((visibility("default"))) int32_t ar_kat_math_setmaxnreg(int32_t realloc, int32_t iters,
-                                                                                 unsigned long long* cycles,
-                                                                                 uint32_t* sink, void* stream) {
-  ar::kat_math_setmaxnreg_kernel<<<148, 512, 0, (cudaStream_t)stream>>>(realloc, iters, 0.1275f, 1.0f, 0.25f,
-                                                                        cycles, sink);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
-}

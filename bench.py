@@ -1,22 +1,31 @@
-"""Benchmark of the attention forward+backward path (BASELINE config 2 per GPU).
+"""Benchmark of the attention forward+backward path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 2|4] [--impl reference]
 
-One step = the SSSL group of the default model: four attention layers of B=16, H=4, T=2048,
-head_dim=128 (bf16 operands, fp32 accumulate, RoPE base 10000 applied to Q/K), three with a
-1024-key sliding window and one full causal, forward for all four then backward for all four.
-Each layer has its own Q/K/V/dO/O/gradient tensors (1.4 GB per GPU in total, far beyond the
-126 MB L2).  Under torchrun every rank runs the same per-GPU workload on its own (batch, head)
-units (weak scaling, no data-path collective); the time is the max over ranks of a
-CUDA-event interval and the value is the whole-job algorithmic TFLOP/s
-(14 * D * visible (q,k) pairs * B * H per layer).
+Default (--config 2, BASELINE config 2 per GPU): one step = the SSSL group of the default model:
+four attention layers of B=16, H=4, T=2048, head_dim=128 (bf16 operands, fp32 accumulate, RoPE base
+10000 applied to Q/K, fp32 gradients), three with a 1024-key sliding window and one full causal,
+forward for all four then backward for all four.  Each layer has its own Q/K/V/dO/O/gradient
+tensors (1.4 GB per GPU in total, far beyond the 126 MB L2).  Under torchrun every rank runs the
+same per-GPU workload on its own (batch, head) units (weak scaling, no data-path collective); the
+time is the max over ranks of a CUDA-event interval and the value is the whole-job algorithmic
+TFLOP/s (14 * D * visible (q,k) pairs * B * H per layer).
+
+--config 4 (BASELINE config 4, long context): B=4, H=16, T=8192; the 1024-key window and the full
+causal mask are timed separately (`value` is the windowed one, `full_causal` the other).
+
+Besides the headline the line carries: `roofline` (per-kernel achieved TFLOP/s against the measured
+bf16 peak), `sustained` (the same step back to back for at least three seconds, with the clocks
+seen), `config5` (BASELINE config 5: the global B=128, H=8 workload split over the ranks by
+(batch, head) units, strong scaling), `e2e` (host buffers in, host buffers out) and, on one GPU,
+`cpu_baseline` (the reference's algorithm on the host cores).
 """
 from __future__ import annotations
 
 import argparse
+import copy
 import json
 import os
-import subprocess
 import sys
 import time
 
@@ -24,9 +33,26 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-B, H, T, D = 16, 4, 2048, 128
-WINDOWS = (1024, 1024, 1024, 2048)      # config.mojo:49-55 with sequence_len 2048, one SSSL group
+D = 128
 METRIC = "attn_fwd_bwd_tflops_windowed_causal"
+# name -> (B per GPU, H, T, per-layer windows of one step)
+CONFIGS = {
+    2: dict(B=16, H=4, T=2048, windows=(1024, 1024, 1024, 2048),      # config.mojo:49-55, one SSSL group
+            workload="BASELINE config 2 per GPU: default-model attention fwd+bwd, SSSL group "
+                     "(3 x window 1024 + 1 x full causal), RoPE on Q/K"),
+    4: dict(B=4, H=16, T=8192, windows=(1024,),
+            workload="BASELINE config 4 per GPU: long-context attention fwd+bwd, T=8192, window 1024 "
+                     "(full causal timed separately), RoPE on Q/K"),
+}
+C5 = dict(B=128, H=8, T=2048, windows=(1024, 1024, 1024, 2048))       # BASELINE config 5 (global)
+
+# DRAM bytes per launch (dram__bytes_read.sum, dram__bytes_write.sum) from an ncu capture of
+# full-size launches: B=16, H=4, T=2048, W=1024, 64 (b,h) units; other unit counts scale it.
+NCU_DRAM = {
+    "attn_fwd": (125.0e6, 13.0e6), "attn_bwd_dq": (253.7e6, 40.0e6), "attn_bwd_dkv": (159.9e6, 82.3e6),
+    "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:attn_ "
+              "on one forward+backward of B=16 H=4 T=2048 W=1024 (per launch; scaled by the unit count)",
+}
 
 
 def pairs(t: int, w: int) -> int:
@@ -36,12 +62,8 @@ def pairs(t: int, w: int) -> int:
     return (w + 1) * (w + 2) // 2 + (t - w - 1) * (w + 1)
 
 
-def layer_flops(w: int, per_pair: int, b: int = B, h: int = H) -> float:
-    return float(per_pair) * D * pairs(T, w) * b * h
-
-
-def step_flops(b: int = B, h: int = H) -> float:
-    return sum(layer_flops(w, 14, b, h) for w in WINDOWS)
+def flops(per_pair: int, t: int, windows, b: int, h: int) -> float:
+    return sum(float(per_pair) * D * pairs(t, w) * b * h for w in windows)
 
 
 def measured_peaks():
@@ -54,7 +76,7 @@ def measured_peaks():
 
 class ClockSampler:
     """SM clock and throttle-reason samples (read-only NVML queries, every 20 ms) taken by a
-    background thread while the timed region runs."""
+    background thread while a timed region runs."""
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
                0x4: "sw_power_cap"}
 
@@ -97,31 +119,37 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # CPU arm: the oracle port (the reference has no CPU implementation and cannot be built)
 # --------------------------------------------------------------------------------------
-CPU_SAMPLE_B, CPU_SAMPLE_H = 2, 4   # 8 of the 64 (b,h) units of the workload, all four layers
+def cpu_sample(cfg_id: int):
+    """A bounded sample of the workload: whole (b, h) units, all layers of the step."""
+    c = CONFIGS[cfg_id]
+    if cfg_id == 2:
+        return dict(B=2, H=4, T=c["T"], windows=c["windows"], of=f"8 of {c['B'] * c['H']} units")
+    return dict(B=1, H=2, T=c["T"], windows=c["windows"], of=f"2 of {c['B'] * c['H']} units")
 
 
-def cpu_sample_inputs():
+def cpu_sample_inputs(s):
     from oracle import oracle as orc
     orc.use_all_cores()
-    q, k, v, do = orc.make_inputs(CPU_SAMPLE_B, T, CPU_SAMPLE_H, D, seed=0, bf16=True)
-    return orc, (q, k, v, do), orc.rope_table(T, D)
+    q, k, v, do = orc.make_inputs(s["B"], s["T"], s["H"], D, seed=0, bf16=True)
+    return orc, (q, k, v, do), orc.rope_table(s["T"], D)
 
 
-def cpu_time_once(orc, tensors, tables) -> float:
+def cpu_time_once(orc, tensors, tables, windows) -> float:
     t0 = time.perf_counter()
-    for w in WINDOWS:
+    for w in windows:
         orc.attention_path(*tensors[:3], tensors[3], w, rope=tables)
     return time.perf_counter() - t0
 
 
-def cpu_baseline():
-    orc, tensors, tables = cpu_sample_inputs()
-    cpu_time_once(orc, tensors, tables)                      # warm-up (page-in, thread pool)
-    dt = min(cpu_time_once(orc, tensors, tables) for _ in range(2))
-    flops = step_flops(CPU_SAMPLE_B, CPU_SAMPLE_H)
-    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port",
-            "sample": f"oracle port, B={CPU_SAMPLE_B} H={CPU_SAMPLE_H} T={T} D={D}, SSSL group "
-                      f"(8 of 64 units), fwd+bwd, {dt:.2f} s"}
+def cpu_baseline(cfg_id: int):
+    s = cpu_sample(cfg_id)
+    orc, tensors, tables = cpu_sample_inputs(s)
+    cpu_time_once(orc, tensors, tables, s["windows"])                      # warm-up (page-in, thread pool)
+    dt = min(cpu_time_once(orc, tensors, tables, s["windows"]) for _ in range(2))
+    return {"value": flops(14, s["T"], s["windows"], s["B"], s["H"]) / dt / 1e12, "unit": "TFLOP/s",
+            "cores": orc.num_threads(), "kind": "port",
+            "sample": f"oracle port, B={s['B']} H={s['H']} T={s['T']} D={D}, windows {list(s['windows'])} "
+                      f"({s['of']}), fwd+bwd, {dt:.2f} s"}
 
 
 def run_reference(args):
@@ -131,26 +159,25 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    orc, tensors, tables = cpu_sample_inputs()
+    s = cpu_sample(args.config)
+    orc, tensors, tables = cpu_sample_inputs(s)
     for _ in range(min(args.warmup, 2)):
-        cpu_time_once(orc, tensors, tables)
+        cpu_time_once(orc, tensors, tables, s["windows"])
     steps = max(1, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(steps):
-        cpu_time_once(orc, tensors, tables)
+        cpu_time_once(orc, tensors, tables, s["windows"])
     dt = (time.perf_counter() - t0) / steps
-    flops = step_flops(CPU_SAMPLE_B, CPU_SAMPLE_H)
-    val = flops / dt / 1e12
+    val = flops(14, s["T"], s["windows"], s["B"], s["H"]) / dt / 1e12
     cb = {"value": val, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port",
-          "sample": f"B={CPU_SAMPLE_B} H={CPU_SAMPLE_H} T={T} D={D} SSSL group per step (8 of 64 units)"}
+          "sample": f"B={s['B']} H={s['H']} T={s['T']} D={D} windows {list(s['windows'])} per step ({s['of']})"}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "default-model attention fwd+bwd, SSSL group, T=2048 hd=128 "
-                               "(bounded sample of B=16 H=4)", "B": CPU_SAMPLE_B, "H": CPU_SAMPLE_H, "T": T,
-                   "D": D, "windows": list(WINDOWS)},
-        "tokens_per_s": CPU_SAMPLE_B * T * len(WINDOWS) / dt,
+        "config": {"workload": CONFIGS[args.config]["workload"] + " (bounded sample)", "B": s["B"], "H": s["H"],
+                   "T": s["T"], "D": D, "windows": list(s["windows"])},
+        "tokens_per_s": s["B"] * s["T"] * len(s["windows"]) / dt,
         "cpu_baseline": cb,
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -159,6 +186,33 @@ def run_reference(args):
 # --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(local: int):
+    """Best effort: run this rank (and so allocate its pinned host buffers) on the CPUs of the NUMA
+    node its GPU hangs off, so that eight ranks do not all stage through one memory controller.
+    Returns a short description for the output line; failing at any step leaves things as they are."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return "numa node unknown"
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return f"gpu on node {node}, none of its cpus allowed here"
+        os.sched_setaffinity(0, allowed)
+        return f"bound to node {node} ({len(allowed)} cpus)"
+    except Exception as e:  # noqa: BLE001
+        return "not bound: " + type(e).__name__
+
+
 def run_gpu(args):
     import torch
 
@@ -170,6 +224,7 @@ def run_gpu(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    numa = bind_to_gpu_numa_node(local)
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
@@ -178,40 +233,45 @@ def run_gpu(args):
     dev = torch.device("cuda", local)
     ab.lib()  # fail loudly if libarattn.so is missing
 
+    cfg = CONFIGS[args.config]
+    B, H, T = args.batch or cfg["B"], cfg["H"], cfg["T"]
+    windows = cfg["windows"]
+    nl = len(windows)
     cos_h, sin_h = ab.precompute_rope(T, D)
     tables = (torch.from_numpy(cos_h).to(dev), torch.from_numpy(sin_h).to(dev))
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    nl = len(WINDOWS)
+    peak_burst, peak_sust, hbm_gbs, peak_src = measured_peaks()
 
-    def randn():
-        return torch.randn(B, T, H, D, device=dev, generator=gen).to(torch.bfloat16)
+    def randn(b, t, h):
+        return torch.randn(b, t, h, D, device=dev, generator=gen).to(torch.bfloat16)
 
-    layers = []
-    for w in WINDOWS:
-        L = {"w": w, "q": randn(), "k": randn(), "v": randn(), "do": randn()}
+    def make_layer(b, t, h, w, grad_dtype=torch.float32):
+        L = {"w": w, "q": randn(b, t, h), "k": randn(b, t, h), "v": randn(b, t, h), "do": randn(b, t, h)}
         L["o"] = torch.empty_like(L["q"])
-        L["lse"] = torch.empty(B, T, H, device=dev, dtype=torch.float32)
-        L["d"] = torch.empty(B, T, H, device=dev, dtype=torch.float32)
+        L["lse"] = torch.empty(b, t, h, device=dev, dtype=torch.float32)
+        L["d"] = torch.empty(b, t, h, device=dev, dtype=torch.float32)
         for n in ("dq", "dk", "dv"):
-            L[n] = torch.empty(B, T, H, D, device=dev, dtype=torch.float32)
+            L[n] = torch.empty(b, t, h, D, device=dev, dtype=grad_dtype)
         if args.rope == "saved":      # the reference's data flow: rotate once, save, reuse in backward
             L["q_rot"], L["k_rot"] = torch.empty_like(L["q"]), torch.empty_like(L["k"])
-        L["p"] = ab.AttnParams(window=w, rope=tables, rope_prepass=args.rope == "prepass",
+        L["p"] = ab.AttnParams(window=w, rope=tables, rope_prepass=args.rope == "prepass", grad_dtype=grad_dtype,
                                q_rot=L.get("q_rot"), k_rot=L.get("k_rot"))
-        layers.append(L)
+        return L
 
-    def fwd(L):
-        ab.attn_fwd(L["q"], L["k"], L["v"], L["p"], out=L["o"], lse=L["lse"])
+    def fwd(L, p=None):
+        ab.attn_fwd(L["q"], L["k"], L["v"], p or L["p"], out=L["o"], lse=L["lse"])
 
     def bwd(L, p=None):
         ab.attn_bwd(L["q"], L["k"], L["v"], L["o"], L["do"], L["lse"], p or L["p"], d_buf=L["d"],
                     dq=L["dq"], dk=L["dk"], dv=L["dv"])
 
-    def step():
-        for L in layers:
-            fwd(L)
-        for L in reversed(layers):
-            bwd(L)
+    def make_step(layers):
+        def step():
+            for L in layers:
+                fwd(L)
+            for L in reversed(layers):
+                bwd(L)
+        return step
 
     def barrier():
         if dist is not None:
@@ -229,71 +289,167 @@ def run_gpu(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1)
 
-    for _ in range(max(args.warmup, 3)):
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def check_status():
+        if _lib.lib().ar_device_status() != _lib.AR_OK:
+            raise SystemExit("device status: " + _lib.lib().ar_last_error().decode())
+
+    # ---- headline: K steps, barrier + synchronize on both sides, max over ranks ----------------
+    layers = [make_layer(B, T, H, w) for w in windows]
+    step = make_step(layers)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
     ms_total = timed(step, args.steps)
     barrier()
     clocks = sampler.stop() if sampler else None
-    if _lib.lib().ar_device_status() != _lib.AR_OK:
-        raise SystemExit("device status: " + _lib.lib().ar_last_error().decode())
-    if dist is not None:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    value = step_flops() * world / (ms_step * 1e-3) / 1e12
+    check_status()
+    ms_step = max_over_ranks(ms_total) / args.steps
+    step_fl = flops(14, T, windows, B, H)
+    value = step_fl * world / (ms_step * 1e-3) / 1e12
+    line_extra = {}
 
-    # ---- per-kernel device times (same tensors, same stream) for the roofline -----------
-    import copy
-    reps = 5
-    phase = {}
-    phase["attn_fwd"] = timed(lambda: [fwd(L) for L in layers], reps) / reps
+    # ---- config 4 only: the full causal mask, timed the same way -----------------------------
+    if args.config == 4:
+        full = [make_layer(B, T, H, 0)]
+        fstep = make_step(full)
+        for _ in range(3):
+            fstep()
+        barrier()
+        ms_full = max_over_ranks(timed(fstep, args.steps)) / args.steps
+        fl_full = flops(14, T, (0,), B, H)
+        line_extra["full_causal"] = {"value": fl_full * world / (ms_full * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                     "ms_per_step": ms_full, "frac_of_burst_peak": fl_full / (ms_full * 1e-3) / 1e12 / peak_burst,
+                                     "tokens_per_s": world * B * T / (ms_full * 1e-3)}
+        del full, fstep
+        check_status()
 
-    def only(**kw):
-        ps = []
-        for L in layers:
-            p = copy.copy(L["p"])
-            p.skip_d, p.skip_dq, p.skip_dkv = kw.get("d", True), kw.get("dq", True), kw.get("dkv", True)
-            ps.append(p)
-        return lambda: [bwd(L, p) for L, p in zip(layers, ps)]
+    # ---- per-kernel device times (same tensors, same stream) for the roofline -----------------
+    roofline = None
+    if not args.no_phases:
+        reps = 5
 
-    prepass_ms = timed(only(), reps) / reps                      # rope pre-pass of q, k alone (none in "saved" mode)
-    # In the step the dQ kernel also computes D = rowsum(O*dO) and the key-stationary statistics the
-    # dK/dV kernel streams; timed alone, the dK/dV launch is preceded by the stand-alone re-layout.
-    phase["attn_bwd_dq(+D)"] = timed(only(d=False, dq=False), reps) / reps - prepass_ms
-    phase["attn_bwd_dkv(+stats_relayout)"] = timed(only(dkv=False), reps) / reps - prepass_ms
-    # executed-useful FLOPs per kernel on exact visible pairs: fwd QK^T+PV = 4D; dq kernel
-    # S, dP, dQ = 6D; dkv kernel S^T, dP^T, dV, dK = 8D (S and dP are recomputed in both).
-    per_pair = {"attn_fwd": 4, "attn_bwd_dq(+D)": 6, "attn_bwd_dkv(+stats_relayout)": 8}
-    dominant = max(per_pair, key=lambda n: phase[n])
-    dom_flops = sum(layer_flops(w, per_pair[dominant]) for w in WINDOWS)   # 4 launches
-    dom_ms_per_launch = phase[dominant] / nl
-    peak_burst, peak_sust, hbm_gbs, peak_src = measured_peaks()
-    achieved = dom_flops / nl / (dom_ms_per_launch * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak_sust,
-                "unit": "TFLOP/s", "frac": achieved / peak_sust,
-                # DRAM bytes per launch of the dK/dV kernel: ncu capture of a full-size launch
-                # (64 (b,h) units, window 1024: 159.9 MB read + 82.3 MB written before the kernel
-                # ended, profiles/); other unit counts scale it
-                "traffic": (242.2e6 * (B * H) / 64.0) if dominant.startswith("attn_bwd_dkv") else None,
-                "peak_source": f"bf16_tflops_sustained, {peak_src} (kernel timed inside a long loop)",
-                "frac_of_burst_peak": achieved / peak_burst,
-                "launch_ms": dom_ms_per_launch,
-                "phase_ms_per_step": {k: round(v, 4) for k, v in phase.items()}}
+        def only(**kw):
+            ps = []
+            for L in layers:
+                p = copy.copy(L["p"])
+                p.skip_d, p.skip_dq, p.skip_dkv = kw.get("d", True), kw.get("dq", True), kw.get("dkv", True)
+                ps.append(p)
+            return lambda: [bwd(L, p) for L, p in zip(layers, ps)]
+
+        # forward on Q, K that are already rotated: the attention kernel without the rotation launch
+        plain = [ab.AttnParams(window=L["w"]) for L in layers]
+        phase = {"attn_fwd": timed(lambda: [fwd(L, p) for L, p in zip(layers, plain)], reps) / reps}
+        phase["fwd_total(rope+attn_fwd)"] = timed(lambda: [fwd(L) for L in layers], reps) / reps
+        prepass_ms = timed(only(), reps) / reps                      # rope pre-pass of q, k alone (none in "saved" mode)
+        # In the step the dQ kernel also computes D = rowsum(O*dO) and the key-stationary statistics the
+        # dK/dV kernel streams; timed alone, the dK/dV launch is preceded by the stand-alone re-layout.
+        phase["attn_bwd_dq"] = timed(only(d=False, dq=False), reps) / reps - prepass_ms
+        phase["attn_bwd_dkv"] = timed(only(dkv=False), reps) / reps - prepass_ms
+        check_status()
+        # Peak: the burst figure while the sampled clock sat at its maximum with no power-cap bit,
+        # the sustained one when the power cap was seen (these short loops run at the burst clock).
+        capped = bool(clocks and "sw_power_cap" in clocks.get("reasons", []))
+        peak, peak_name = (peak_sust, "bf16_tflops_sustained") if capped else (peak_burst, "bf16_tflops")
+        # executed-useful FLOPs per kernel on exact visible pairs: fwd QK^T+PV = 4D; dq kernel
+        # S, dP, dQ = 6D; dkv kernel S^T, dP^T, dV, dK = 8D (S and dP are recomputed in both).
+        per_pair = {"attn_fwd": 4, "attn_bwd_dq": 6, "attn_bwd_dkv": 8}
+        kernels = {}
+        for name, pp in per_pair.items():
+            ach = flops(pp, T, windows, B, H) / (phase[name] * 1e-3) / 1e12
+            rd, wr = NCU_DRAM[name]
+            kernels[name] = {"flop_per_pair": pp * D, "ms_per_step": round(phase[name], 4), "launches_per_step": nl,
+                             "achieved": ach, "frac": ach / peak,
+                             "traffic": (rd + wr) * (B * H) / 64.0 if T == 2048 else None}
+        rope_ms = phase["fwd_total(rope+attn_fwd)"] - phase["attn_fwd"]
+        if args.rope == "saved" and rope_ms > 0:
+            # forward rotation of Q and K (one launch per layer): 2 tensors read + 2 written, bf16
+            nbytes = 4 * B * T * H * D * 2 * nl
+            kernels["rope_pair_bf16_128"] = {"bound": "hbm", "ms_per_step": round(rope_ms, 4), "launches_per_step": nl,
+                                             "achieved": nbytes / (rope_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                             "frac": nbytes / (rope_ms * 1e-3) / 1e9 / hbm_gbs, "peak": hbm_gbs}
+        dominant = max(per_pair, key=lambda n: phase[n])
+        kd = kernels[dominant]
+        roofline = {"bound": "tensor", "kernel": dominant, "achieved": kd["achieved"], "peak": peak, "unit": "TFLOP/s",
+                    "frac": kd["frac"], "traffic": kd["traffic"], "traffic_source": NCU_DRAM["source"],
+                    "peak_source": f"{peak_name}, {peak_src}" + (" (sw_power_cap sampled)" if capped else
+                                                                 " (clock at max, no power-cap bit sampled)"),
+                    "launch_ms": phase[dominant] / nl,
+                    "kernels": kernels,
+                    # the whole path on the 14*D the metric credits (the split backward executes 14*D
+                    # for its 10*D), against the same peak
+                    "path": {"flop_per_pair_credited": 14 * D, "flop_per_pair_executed": 18 * D,
+                             "achieved": value / world, "frac": value / world / peak}}
+
+    # ---- sustained: the same step back to back for at least three seconds ------------------------
+    sustained = None
+    if not args.no_sustained:
+        n_sus = max(args.steps, int(3000.0 / ms_step) + 1)
+        barrier()
+        s2 = ClockSampler(local) if rank == 0 else None
+        ms_sus = max_over_ranks(timed(step, n_sus)) / n_sus
+        ck = s2.stop() if s2 else None
+        check_status()
+        tf = step_fl * world / (ms_sus * 1e-3) / 1e12
+        sustained = {"value": tf, "unit": "TFLOP/s", "steps": n_sus, "ms_per_step": ms_sus, "seconds": ms_sus * n_sus * 1e-3}
+        if ck and ck.get("sm_mhz"):
+            sustained.update({"sm_mhz_median": ck["sm_mhz"], "sm_max_mhz": ck["sm_max_mhz"], "reasons": ck["reasons"],
+                              "power_capped": "sw_power_cap" in ck["reasons"],
+                              "value_at_max_clock": tf * ck["sm_max_mhz"] / ck["sm_mhz"],
+                              "frac_of_sustained_peak": tf / world / peak_sust})
+
+    # ---- BASELINE config 5: the global B=128, H=8 workload sharded over the ranks -----------------
+    config5 = None
+    if args.config == 2 and not args.no_config5 and not args.batch:
+        del layers, step
+        torch.cuda.empty_cache()
+        b0, nb, h0, nh = ab.shard_units(C5["B"], C5["H"], world, rank)    # contiguous batch slab, all heads
+        assert nh == C5["H"] and h0 == 0
+        L5 = make_layer(nb, C5["T"], C5["H"], 0)        # one tensor set (0.4 GB per tensor at N=1, beyond L2)
+        ps = [copy.copy(L5["p"]) for _ in C5["windows"]]
+        for p, w in zip(ps, C5["windows"]):
+            p.window = w
+
+        def step5():
+            for p in ps:
+                fwd(L5, p)
+            for p in reversed(ps):
+                bwd(L5, p)
+
+        for _ in range(3):
+            step5()
+        barrier()
+        n5 = max(3, min(args.steps, 10))
+        ms5 = max_over_ranks(timed(step5, n5)) / n5
+        barrier()
+        check_status()
+        fl5 = flops(14, C5["T"], C5["windows"], C5["B"], C5["H"])
+        config5 = {"workload": "BASELINE config 5: B=128 H=8 T=2048 D=128 bf16, SSSL group, (batch, head) units "
+                               f"split over {world} rank(s) in contiguous batch slabs, no collective",
+                   "scaling": "strong", "units_total": C5["B"] * C5["H"], "units_per_rank": nb * nh,
+                   "ms_per_step": ms5, "value": fl5 / (ms5 * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "tokens_per_s": C5["B"] * C5["T"] * len(C5["windows"]) / (ms5 * 1e-3), "steps": n5}
+        del L5
+        torch.cuda.empty_cache()
+        layers = [make_layer(B, T, H, w) for w in windows] if not args.no_e2e else None
 
     # ---- end to end: host buffers -> H2D -> fwd+bwd through the public API -> D2H --------
     e2e = None
     if not args.no_e2e:
-        host_in = [{n: torch.empty(B, T, H, D, dtype=torch.bfloat16).pin_memory() for n in ("q", "k", "v", "do")}
-                   for _ in layers]
+        gb = torch.bfloat16
+        host_in = [{n: torch.empty(B, T, H, D, dtype=gb).pin_memory() for n in ("q", "k", "v", "do")} for _ in windows]
         for hl, L in zip(host_in, layers):
             for n in hl:
                 hl[n].copy_(L[n])
-        gb = torch.bfloat16
-        host_out = [{n: torch.empty(B, T, H, D, dtype=gb).pin_memory() for n in ("o", "dq", "dk", "dv")}
-                    for _ in layers]
+        host_out = [{n: torch.empty(B, T, H, D, dtype=gb).pin_memory() for n in ("o", "dq", "dk", "dv")} for _ in windows]
 
         # Two complete device buffer sets (inputs, saved rotated Q/K, O, LSE, D, bf16 gradients), used
         # by alternate steps, and three streams: while one step's kernels run, the next step's inputs
@@ -302,7 +458,7 @@ def run_gpu(args):
         # the last device->host copy has finished.
         def make_set():
             st = []
-            for w in WINDOWS:
+            for w in windows:
                 S = {n: torch.empty(B, T, H, D, device=dev, dtype=gb) for n in
                      ("q", "k", "v", "do", "o", "dq", "dk", "dv", "q_rot", "k_rot")}
                 S["lse"] = torch.empty(B, T, H, device=dev, dtype=torch.float32)
@@ -316,8 +472,8 @@ def run_gpu(args):
         sets = [make_set(), make_set()]
         s_main = torch.cuda.current_stream()
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-        ev_in = [[torch.cuda.Event() for _ in layers] for _ in range(2)]
-        ev_bwd = [[torch.cuda.Event() for _ in layers] for _ in range(2)]
+        ev_in = [[torch.cuda.Event() for _ in windows] for _ in range(2)]
+        ev_bwd = [[torch.cuda.Event() for _ in windows] for _ in range(2)]
         ev_free = [torch.cuda.Event() for _ in range(2)]     # the set's results have left the device
         for e in ev_free:
             e.record(s_main)
@@ -359,20 +515,18 @@ def run_gpu(args):
         e2e_steps = max(2, min(args.steps, 10))
         e2e_run(2)
         barrier()
-        ms_e2e = e2e_run(e2e_steps)
-        if dist is not None:
-            t = torch.tensor([ms_e2e], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms_e2e = float(t.item())
-        ms_e2e /= e2e_steps
+        ms_e2e = max_over_ranks(e2e_run(e2e_steps)) / e2e_steps
+        check_status()
         nbytes = B * T * H * D * 2
-        e2e = {"value": step_flops() * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+        e2e = {"value": step_fl * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": 4 * nl * nbytes, "d2h_bytes_per_step": 4 * nl * nbytes,
                "ms_per_step": ms_e2e, "tokens_per_s": world * B * T * nl / (ms_e2e * 1e-3),
+               "host_copy_gbs_per_gpu_each_way": 4 * nl * nbytes / (ms_e2e * 1e-3) / 1e9, "host_numa": numa,
                "note": "pinned host q,k,v,dO in; o,dq,dk,dv (bf16) out; steps pipelined over two device "
-                       "buffer sets and three streams (H2D, kernels, D2H); timed until the last D2H copy is done"}
+                       "buffer sets and three streams (H2D, kernels, D2H); timed until the last D2H copy is done; "
+                       "bound by the host<->device copies, not by the kernels"}
 
-    cpu = cpu_baseline() if (rank == 0 and world == 1 and not args.no_cpu) else None
+    cpu = cpu_baseline(args.config) if (rank == 0 and world == 1 and not args.no_cpu) else None
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -384,25 +538,26 @@ def run_gpu(args):
     launches_per_step = nl * ((1 + (0 if args.rope == "fused" else 1)) + 2 + (0 if args.rope == "saved" else 1))
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "BASELINE config 2 per GPU: default-model attention fwd+bwd, SSSL group "
-                               "(3 x window 1024 + 1 x full causal), RoPE on Q/K",
-                   "B_per_gpu": B, "H": H, "T": T, "D": D, "windows": list(WINDOWS), "global_batch": B * world,
+        "config": {"workload": cfg["workload"],
+                   "B_per_gpu": B, "H": H, "T": T, "D": D, "windows": list(windows), "global_batch": B * world,
                    "grad_dtype": "f32", "rope": {"saved": "fwd: rotate Q/K once into saved bf16 buffers; bwd: reuse them, inverse rotation fused into dQ/dK stores",
                             "fused": "fwd: rotate-on-load; bwd: pre-pass + fused inverse",
                             "prepass": "pre-pass in both passes"}[args.rope],
                    "parallelism": f"(batch,head) units sharded over {world} rank(s), no collective",
-                   "l2": "working set 1.4 GB per GPU (inputs larger than L2), distinct tensors per layer"},
+                   "l2": f"working set {(5 * 2 + 2 * 2 + 3 * 4) * B * T * H * D * nl / 1e9:.1f} GB per GPU (inputs larger than L2), "
+                         "distinct tensors per layer"},
         "tokens_per_s": world * B * T * nl / (ms_step * 1e-3),
-        "frac_of_peak": {"burst_1672": value / world / peak_burst, "sustained_1384": value / world / peak_sust,
-                         "nominal_2250": value / world / 2250.0},
-        "roofline": roofline, "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
+        "frac_of_peak": {"burst": value / world / peak_burst, "sustained": value / world / peak_sust,
+                         "nominal_2250": value / world / 2250.0, "source": peak_src},
+        "clocks": clocks, "gpu_launches": launches_per_step * args.steps,
     }
-    if e2e is not None:
-        line["e2e"] = e2e
-    if cpu is not None:
-        line["cpu_baseline"] = cpu
+    line.update(line_extra)
+    for key, obj in (("roofline", roofline), ("sustained", sustained), ("config5", config5), ("e2e", e2e),
+                     ("cpu_baseline", cpu)):
+        if obj is not None:
+            line[key] = obj
     print(json.dumps(line))
 
 
@@ -412,12 +567,19 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS),
+                    help="BASELINE config: 2 = default-model SSSL group (the headline), 4 = long context T=8192")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="batch per GPU instead of the config's (a small case for profilers); 0 = the config's")
     ap.add_argument("--rope", default="saved", choices=["saved", "fused", "prepass"],
                     help="saved: forward rotates Q/K once into saved buffers that backward reuses; "
                          "fused: forward rotates on load, backward rotates in a pre-pass; "
                          "prepass: both passes rotate in a pre-pass")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-phases", action="store_true", help="skip the per-kernel timing behind `roofline`")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the three-second back-to-back run")
+    ap.add_argument("--no-config5", action="store_true", help="skip the config-5 strong-scaling object")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -69,6 +69,15 @@ AR_API const char* ar_last_error(void);
  * Synchronises the device. */
 AR_API ar_status ar_device_status(void);
 
+/* No counterpart in the reference: lets an integrator exercise the handling of AR_ERR_TIMEOUT
+ * without a misbehaving GPU.  Enqueues a one-warp kernel whose bounded wait (on a barrier that
+ * nothing arrives at) is cut to about a millisecond; it runs out, sets the status word the way an
+ * abandoned wait inside an attention kernel does, and the kernel returns normally - nothing
+ * faults, traps or hangs.  which = 0 sets the word ar_device_status() reads, which = 1 the word
+ * ar_noalloc_status() reads.  Until that word is read (and thereby cleared) every attention
+ * kernel launched on the device returns at once without touching its outputs. */
+AR_API ar_status ar_selftest_wait_timeout(int32_t which, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * (i) Exact mirrors of kernels/ops.mojo: fp32 tensors, same argument order, `Int`
  *     dims as int64_t, plus a trailing stream.  The attention mirrors stage their
@@ -90,6 +99,25 @@ AR_API ar_status ar_rope_fwd(float* out, const float* in, const float* cos_buf,
 AR_API ar_status ar_rope_bwd(float* grad_in, const float* grad_out, const float* cos_buf,
                              const float* sin_buf, int64_t num_tokens, int64_t num_heads,
                              int64_t head_dim, int64_t seq_len, void* stream);
+
+/* The step before attention in one launch: replaces the two rope_fwd launches and the two per-head
+ * rmsnorm_fwd launches on q and k (model.mojo:668-687; ops.mojo:209-217, 61-67) and writes the
+ * bf16 operands the fused family reads, so that the trainer's fp32 q, k, v (outputs of its QKV
+ * projections, model.mojo:643-645) reach the tensor-core kernels with one pass over memory:
+ *     q_rot = bf16( rope(q) / sqrt(mean(rope(q)^2) + eps) )   per (token, head) row, same for k
+ *     v_bf16 = bf16(v)                                       (v, v_bf16 may both be NULL)
+ * q_rot, k_rot, v_bf16: bf16 [num_tokens, num_heads, 128].  rms_q, rms_k (optional, fp32
+ * [num_tokens, num_heads]) receive the row's sqrt(mean + eps), rmsnorm_fwd's rms_out.  eps is the
+ * reference's 1e-5 (ops.mojo:97).  Position index as in ar_rope_fwd (seq_len).  Afterwards call
+ * ar_attn_fwd with rope_mode 0 on (q_rot, k_rot, v_bf16); for the backward pass hand the same
+ * q_rot, k_rot to ar_attn_bwd with rope_mode 1, which then returns dq, dk with rope_bwd applied -
+ * what the reference computes, whose backward passes gradients straight through this
+ * normalisation (model.mojo:937). */
+AR_API ar_status ar_qk_norm_rope_cast(void* q_rot, void* k_rot, void* v_bf16, float* rms_q,
+                                      float* rms_k, const float* q, const float* k, const float* v,
+                                      const float* cos_buf, const float* sin_buf,
+                                      int64_t num_tokens, int64_t num_heads, int64_t head_dim,
+                                      int64_t seq_len, float eps, void* stream);
 
 /* replaces flash_attn_fwd (ops.mojo:244-255; launched at model.mojo:694-699).
  * q, k are the already-rotated tensors. */
@@ -115,12 +143,21 @@ AR_API ar_status ar_flash_attn_fwd(float* output, float* lse_out, const float* q
  *     (each call overwrites what it reads, nothing needs clearing).  Calls that overlap on
  *     the GPU (different streams, or threads) race on it: keep them ordered on one stream.
  *   - Its kernels record an abandoned device-side wait in the library's own status symbol,
- *     which ar_device_status() (an allocating call on first use) does not read. */
+ *     which ar_device_status() (an allocating call on first use) does not read: read it with
+ *     ar_noalloc_status().  While that word is set, later allocation-free calls on the device do
+ *     no work (their kernels return at once), so check it wherever the results matter. */
 #define AR_NOALLOC_MAX_ROWS 16384
 AR_API ar_status ar_flash_attn_fwd_noalloc(float* output, float* lse_out, const float* q,
                                            const float* k, const float* v, int64_t B, int64_t T,
                                            int64_t num_heads, int64_t head_dim,
                                            int64_t window_size, void* stream);
+
+/* No counterpart in the reference: the ar_device_status() of the allocation-free entry point.
+ * Waits for the current device, reads the status word that ar_flash_attn_fwd_noalloc's kernels
+ * write and clears it when set; returns AR_ERR_TIMEOUT if a bounded device-side wait was abandoned
+ * since the last call, AR_OK otherwise.  Like the entry point it serves it allocates nothing (the
+ * word is a symbol of the library image; the copies go through cudaMemcpy). */
+AR_API ar_status ar_noalloc_status(void);
 
 /* replaces flash_attn_bwd_precompute_d (ops.mojo:329-337; model.mojo:915-919). */
 AR_API ar_status ar_flash_attn_bwd_precompute_d(float* d_out, const float* output,

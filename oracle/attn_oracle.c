@@ -365,3 +365,43 @@ ORACLE_API void oracle_attention_path(float* o, float* lse, float* d_buf, float*
     oracle_rope_bwd(dk, dk, cos_buf, sin_buf, B * T, H, D, T);
   }
 }
+
+/* ops.mojo:61-104 (rmsnorm_fwd) - y = x / sqrt(mean(x^2) + 1e-5), one block of 256 threads per row.
+ * The sum of squares is formed exactly as the kernel forms it: thread t adds the elements t,
+ * t + 256, ... in order (ops.mojo:77-80); the 256 partial sums are folded in shared memory,
+ * upper half onto lower half, down to 32 (ops.mojo:84-89); the last 32 meet in warp.sum, taken
+ * here as the usual butterfly (offsets 16, 8, 4, 2, 1).  PINNED by the reference's own known-answer
+ * test for this kernel (test_kernels.mojo:140-181: rms = [2.7386, 2.5], out[0,0] = 0.3651,
+ * out[1,3] = 2.0, each within 0.01), checked in tests/test_oracle.py.  In place (out == in) allowed. */
+ORACLE_API void oracle_rmsnorm_fwd(float* out, float* rms_out, const float* in, int64_t num_rows,
+                                   int64_t dim) {
+#pragma omp parallel for schedule(static)
+  for (int64_t row = 0; row < num_rows; ++row) {
+    const float* x = in + row * dim;
+    float part[256];
+    for (int t = 0; t < 256; ++t) {
+      float ss = 0.0f;
+      for (int64_t i = t; i < dim; i += 256) ss += x[i] * x[i];
+      part[t] = ss;
+    }
+    for (int active = 128; active >= 32; active >>= 1)
+      for (int t = 0; t < active; ++t) part[t] += part[t + active];
+    for (int off = 16; off >= 1; off >>= 1)
+      for (int t = 0; t < off; ++t) part[t] += part[t + off];
+    float mean_sq = part[0] / (float)dim;
+    float rms = sqrtf(mean_sq + 1e-5f);
+    if (rms_out) rms_out[row] = rms;
+    for (int64_t i = 0; i < dim; ++i) out[row * dim + i] = x[i] / rms;
+  }
+}
+
+/* The step before attention, in model.mojo's launch order (model.mojo:668-687): rope_fwd in place on
+ * q and k (position = token % seq_len), then rmsnorm_fwd per (token, head) row of head_dim. */
+ORACLE_API void oracle_qk_rope_norm(float* q_out, float* k_out, float* rms_q, float* rms_k, const float* q,
+                                    const float* k, const float* cos_buf, const float* sin_buf,
+                                    int64_t num_tokens, int64_t num_heads, int64_t head_dim, int64_t seq_len) {
+  oracle_rope_fwd(q_out, q, cos_buf, sin_buf, num_tokens, num_heads, head_dim, seq_len);
+  oracle_rope_fwd(k_out, k, cos_buf, sin_buf, num_tokens, num_heads, head_dim, seq_len);
+  oracle_rmsnorm_fwd(q_out, rms_q, q_out, num_tokens * num_heads, head_dim);
+  oracle_rmsnorm_fwd(k_out, rms_k, k_out, num_tokens * num_heads, head_dim);
+}

@@ -95,6 +95,30 @@ def rope_bwd(g: np.ndarray, cos: np.ndarray, sin: np.ndarray, seq_len: int) -> n
     return out
 
 
+def rmsnorm_fwd(x: np.ndarray):
+    """ops.mojo:61-104 on the last axis.  Returns (y, rms) with rms = sqrt(mean(x^2) + 1e-5) per row."""
+    x = np.ascontiguousarray(x, np.float32)
+    dim = x.shape[-1]
+    rows = x.size // dim
+    out = np.empty_like(x)
+    rms = np.empty(x.shape[:-1], np.float32)
+    lib().oracle_rmsnorm_fwd(_p(out), _p(rms), _p(x), _i(rows), _i(dim))
+    return out, rms
+
+
+def qk_rope_norm(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray, seq_len: int):
+    """model.mojo:668-687: rope_fwd then the per-head rmsnorm_fwd on q and k [.., H, D].
+    Returns (q_out, k_out, rms_q, rms_k)."""
+    q, k = (np.ascontiguousarray(a, np.float32) for a in (q, k))
+    H, D = q.shape[-2], q.shape[-1]
+    tokens = q.size // (H * D)
+    qo, ko = np.empty_like(q), np.empty_like(k)
+    rq, rk = np.empty(q.shape[:-1], np.float32), np.empty(k.shape[:-1], np.float32)
+    lib().oracle_qk_rope_norm(_p(qo), _p(ko), _p(rq), _p(rk), _p(q), _p(k), _p(cos), _p(sin), _i(tokens), _i(H),
+                              _i(D), _i(seq_len))
+    return qo, ko, rq, rk
+
+
 def flash_attn_fwd(q, k, v, window_size: int):
     """ops.mojo:244-323.  q,k,v [B,T,H,D] fp32 -> (O [B,T,H,D], LSE [B,T,H])."""
     q, k, v = (np.ascontiguousarray(a, np.float32) for a in (q, k, v))

@@ -50,6 +50,7 @@ def run_fwd(B,H,T,W,c,G=148):
     mk('q_full',1); mk('q_free',2)
     for X in range(2):
         mk(f's_full{X}',1); mk(f'p0_{X}',1); mk(f'p1_{X}',1); mk(f'o_final{X}',1); mk(f'o_free{X}',1); mk(f'exp{X}',1)
+        mk(f'stat{X}',1)
     for s in range(2):
         mk(f'k_full{s}',1); mk(f'k_empty{s}',2); mk(f'v_full{s}',1); mk(f'v_empty{s}',2)
     cnt={'exp0':0,'exp1':0}
@@ -127,10 +128,21 @@ def run_fwd(B,H,T,W,c,G=148):
                 yield ('arrive',f'p0_{X}',1)
                 yield ('cinc',f'exp{X}',1)
                 yield ('arrive',f'p1_{X}',1)
-            yield ('wait',f'o_final{X}',nx&1)
-            yield ('arrive',f'o_free{X}',1)
+            # the row statistics go to the write-out warps; the previous item's have been read
+            if nx>0: yield ('wait',f'o_free{X}',(nx-1)&1)
+            yield ('arrive',f'stat{X}',1)
             g_own+=n_it; g_oth+=n_other; nx+=1; n+=1
-    agents={'tma':tma(),'isA':issuer(0),'isB':issuer(1),'smA':softmax(0),'smB':softmax(1)}
+    def writeout():
+        nxe=[0,0]
+        for item in items_of(c,G,n_items):
+            wi=fwd_item(item,B,H,T,W,n_qb)
+            for X in range(2):
+                if not wi['act'][X]: continue
+                yield ('wait',f'stat{X}',nxe[X]&1)
+                yield ('wait',f'o_final{X}',nxe[X]&1)
+                yield ('arrive',f'o_free{X}',1)
+                nxe[X]+=1
+    agents={'tma':tma(),'isA':issuer(0),'isB':issuer(1),'smA':softmax(0),'smB':softmax(1),'wo':writeout()}
     pending={k:None for k in agents}; done=set(); steps=0
     import random
     order=list(agents)
@@ -187,7 +199,7 @@ def run_dkv(B,H,T,W,c,G=148):
     n_items=((T+127)//128)*B*H
     bars={}
     def mk(n,cnt): bars[n]=Bar(n,cnt)
-    mk('x_full',1); mk('x_free',2); mk('acc_done',2); mk('acc_free',2)
+    mk('x_full',1); mk('x_free',2); mk('acc_done',2); mk('acc_free0',1); mk('acc_free1',1)
     for s in range(4): mk(f'y_full{s}',1); mk(f'y_empty{s}',2)
     for i in range(2): mk(f'g_full{i}',2); mk(f'ready{i}',2)
     def tma():
@@ -206,7 +218,7 @@ def run_dkv(B,H,T,W,c,G=148):
             def acc(it,gg):
                 s=gg%4; bf=gg&1
                 yield ('wait',f'ready{bf}',(gg>>1)&1)
-                if it==0 and n>0: yield ('wait','acc_free',(n-1)&1)
+                if it==0 and n>0: yield ('wait',f'acc_free{I}',(n-1)&1)
                 yield ('arrive',f'y_empty{s}',1)
             yield ('wait','x_full',n&1)
             for it in range(ns):
@@ -228,10 +240,15 @@ def run_dkv(B,H,T,W,c,G=148):
                 yield ('wait',f'g_full{bf}',(gg>>1)&1)
                 yield ('arrive',f'ready{bf}',1)
             g0+=ns
-            yield ('wait','acc_done',n&1)
-            yield ('arrive','acc_free',1)
             n+=1
-    return drive({'tma':tma(),'is0':issuer(0),'is1':issuer(1),'wg0':compute(0),'wg1':compute(1)},bars,f"dkv cta {c}")
+    def store():
+        n=0
+        for item in items_of(c,G,n_items):
+            yield ('wait','acc_done',n&1)
+            yield ('arrive','acc_free0',1)    # dV read
+            yield ('arrive','acc_free1',1)    # dK read
+            n+=1
+    return drive({'tma':tma(),'is0':issuer(0),'is1':issuer(1),'wg0':compute(0),'wg1':compute(1),'st':store()},bars,f"dkv cta {c}")
 def dq_item(item,B,H,T,W,n_qt):
     bh=B*H; qi=item//bh; row0=(n_qt-1-qi)*128
     klo=max(0,row0-W) if W>0 else 0; khi=min(row0+127,T-1)
@@ -241,7 +258,7 @@ def run_dq(B,H,T,W,c,fuse,G=148):
     bars={}
     def mk(n,cnt): bars[n]=Bar(n,cnt)
     mk('x_full',1); mk('x_free',2); mk('g_full',2); mk('g_free',4); mk('ready',4); mk('ds_free',1)
-    mk('acc_done',1); mk('acc_free',2); mk('epi_free',2)
+    mk('acc_done',1); mk('acc_free',1); mk('epi_free',1)
     for s in range(3): mk(f'k_full{s}',1); mk(f'k_empty{s}',2)
     for s in range(2): mk(f'v_full{s}',1); mk(f'v_empty{s}',1); mk(f'd_ready{s}',1); mk(f'd_taken{s}',4)
     def tma():
@@ -254,11 +271,10 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 sk=g%3; sv=g%2
                 yield ('wait',f'k_empty{sk}',((g//3)&1)^1); yield ('arrive',f'k_full{sk}',1)
                 yield ('wait',f'v_empty{sv}',((g//2)&1)^1)
-                if epi_item>=0 and sv==epi_slot:
+                if epi_item>=0 and (sv==epi_slot or it==wi['n_it']-1):
                     yield ('wait','epi_free',epi_item&1); epi_item=-1
                 yield ('arrive',f'v_full{sv}',1)
                 g+=1
-            if epi_item>=0: yield ('wait','epi_free',epi_item&1)
             epi_item=n; epi_slot=(g-1)%2; n+=1
     def issuer(I):
         g=0;n=0
@@ -286,10 +302,17 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 g+=1
             yield ('arrive','acc_done',1); n+=1
     def dwarps():
+        # D of item n (when fused), then the write-out of item n-1
         n=0
         for item in items_of(c,G,n_items):
-            if n>1: yield ('wait',f'd_taken{n&1}',((n>>1)-1)&1)
-            yield ('arrive',f'd_ready{n&1}',1); n+=1
+            if fuse:
+                if n>1: yield ('wait',f'd_taken{n&1}',((n>>1)-1)&1)
+                yield ('arrive',f'd_ready{n&1}',1)
+            if n>0:
+                yield ('wait','acc_done',(n-1)&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
+            n+=1
+        if n>0:
+            yield ('wait','acc_done',(n-1)&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
     def compute(wg):
         g=0;n=0
         for item in items_of(c,G,n_items):
@@ -302,10 +325,7 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 if g>0: yield ('wait','ds_free',(g-1)&1)
                 yield ('arrive','ready',1)
                 g+=1
-            if wg<2:
-                yield ('wait','acc_done',n&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
             n+=1
-    ag={'tma':tma(),'isS':issuer(0),'isP':issuer(1),'isQ':dqiss()}
+    ag={'tma':tma(),'isS':issuer(0),'isP':issuer(1),'isQ':dqiss(),'dw':dwarps()}
     for wg in range(4): ag[f'wg{wg}']=compute(wg)
-    if fuse: ag['dw']=dwarps()
     return drive(ag,bars,f"dq cta {c} fuse {fuse}")

@@ -130,3 +130,34 @@ def test_autograd_agrees_with_manual_backward():
     for n, t in (("dq", tq), ("dk", tk), ("dv", tv)):
         assert orc.parity(got[n], t.grad.numpy())[0] < 2e-5, n
     assert orc.parity(got["o"], o.detach().numpy())[0] < 2e-6
+
+
+def test_rmsnorm_matches_the_reference_known_answer_test():
+    """The reference's own test of rmsnorm_fwd (test_kernels.mojo:140-181): two rows of four values,
+    expected rms = [2.7386, 2.5], out[0,0] = 0.3651, out[1,3] = 2.0, each within 0.01.  This is the
+    one kernel of the step before attention for which the reference holds a known answer."""
+    x = np.array([[1.0, 2.0, 3.0, 4.0], [0.0, 0.0, 0.0, 5.0]], np.float32)
+    y, rms = orc.rmsnorm_fwd(x)
+    assert abs(rms[0] - 2.7386) <= 0.01 and abs(rms[1] - 2.5) <= 0.01
+    assert abs(y[0, 0] - 1.0 / 2.7386) <= 0.01 and abs(y[1, 3] - 5.0 / 2.5) <= 0.01
+    # and exactly: rms = sqrt(mean(x^2) + 1e-5)
+    want = np.sqrt((x.astype(np.float64) ** 2).mean(-1) + 1e-5)
+    assert np.allclose(rms, want, rtol=1e-6)
+    assert np.allclose(y, x / want[:, None], rtol=1e-6)
+
+
+def test_qk_rope_norm_commutes_with_normalising_first():
+    """model.mojo:668-687 rotates q, k and then normalises each head row.  A rotation keeps a row's
+    sum of squares, so normalising first gives the same result up to rounding: the property that lets
+    a caller hand normalised, un-rotated q, k to the fused entry points."""
+    rng = np.random.default_rng(3)
+    B, T, H, D = 2, 33, 3, 128
+    q = rng.standard_normal((B, T, H, D), dtype=np.float32) * 3
+    k = rng.standard_normal((B, T, H, D), dtype=np.float32)
+    cos, sin = orc.rope_table(T, D)
+    qo, ko, rq, rk = orc.qk_rope_norm(q, k, cos, sin, T)
+    qn, rq2 = orc.rmsnorm_fwd(q)
+    assert np.abs(orc.rope_fwd(qn, cos, sin, T) - qo).max() < 2e-6
+    assert np.allclose(rq, rq2, rtol=1e-6)
+    assert np.allclose((qo.astype(np.float64) ** 2).mean(-1), 1.0, atol=1e-4)
+    assert np.allclose((ko.astype(np.float64) ** 2).mean(-1), 1.0, atol=1e-4)

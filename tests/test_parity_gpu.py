@@ -7,7 +7,7 @@ import pytest
 import autoresearch_b200 as ab
 from autoresearch_b200 import _lib
 from oracle import oracle as orc
-from tests.parity_util import assert_parity, compare, device_inputs, rope_tables
+from tests.parity_util import MAX_ABS_TOL, assert_parity, compare, device_inputs, rope_tables
 
 pytestmark = pytest.mark.gpu
 
@@ -18,14 +18,28 @@ def _device_ok():
     assert _lib.lib().ar_device_status() == _lib.AR_OK, _lib.lib().ar_last_error()
 
 
-def run_path(B, T, H, W, rope, dtype, grad_dtype=None, prepass=False, seed=3):
-    """Forward + backward through the fused C-ABI entry points; returns (got, want)."""
+FLOWS = ("fused", "saved", "prepass")
+
+
+def run_path(B, T, H, W, rope, dtype, grad_dtype=None, prepass=False, seed=3, flow="fused"):
+    """Forward + backward through the fused C-ABI entry points; returns (got, want).
+
+    flow picks where RoPE happens (all three give the same results):
+      fused    forward rotates Q/K tiles as they land in shared memory, backward rotates into scratch
+      saved    forward rotates once into caller buffers q_rot / k_rot (the reference's saved_q /
+               saved_k, model.mojo:689-690) which the backward reuses - what bench.py times
+      prepass  both passes rotate into scratch with a separate kernel
+    """
     import torch
     host, dev = device_inputs(B, T, H, seed=seed, dtype=dtype)
     (cos, sin), dtab = rope_tables(T)
     want = orc.attention_path(*host[:3], host[3], W, rope=(cos, sin) if rope else None)
-    p = ab.AttnParams(window=W, rope=dtab if rope else None, rope_prepass=prepass,
-                      grad_dtype=grad_dtype or torch.float32)
+    q_rot = k_rot = None
+    if rope and flow == "saved":
+        q_rot = torch.zeros(B, T, H, 128, device="cuda", dtype=torch.bfloat16)
+        k_rot = torch.zeros_like(q_rot)
+    p = ab.AttnParams(window=W, rope=dtab if rope else None, rope_prepass=prepass or (rope and flow == "prepass"),
+                      grad_dtype=grad_dtype or torch.float32, q_rot=q_rot, k_rot=k_rot)
     o, lse = ab.attn_fwd(*dev[:3], p)
     dq, dk, dv, d = ab.attn_bwd(*dev[:3], o, dev[3], lse, p)
     _device_ok()
@@ -54,15 +68,57 @@ def test_fused_path_bf16(cuda_device, B, T, H, W, rope):
     assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"B{B} T{T} H{H} W{W} rope{rope}")
 
 
+# the multi-item, ragged and many-round shapes again in the two other RoPE flows (the first is the
+# one bench.py times)
+FLOW_CASES = [(2, 200, 3, 0), (1, 640, 2, 129), (2, 1000, 2, 256), (3, 333, 5, 77), (10, 1100, 4, 300),
+              (19, 2049, 5, 100)]
+
+
+@pytest.mark.parametrize("flow", ["saved", "prepass"])
+@pytest.mark.parametrize("B,T,H,W", FLOW_CASES)
+def test_rope_flows_bf16(cuda_device, B, T, H, W, flow):
+    import torch
+    got, want = run_path(B, T, H, W, True, torch.bfloat16, flow=flow)
+    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"B{B} T{T} H{H} W{W} {flow}")
+
+
+def _exact_on_kernel_operands(host, cos, sin, W):
+    """The path in fp64 on the operands the tensor cores actually get: q, k rotated in fp32 and then
+    rounded to bf16.  What separates this from the oracle is the operand rounding alone; what
+    separates the kernels from this is their own arithmetic."""
+    q, k, v, do = host
+    T = q.shape[1]
+    qr = orc.to_bf16_rne(orc.rope_fwd(q, cos, sin, T))
+    kr = orc.to_bf16_rne(orc.rope_fwd(k, cos, sin, T))
+    ex = orc.dense_attention_path(qr, kr, v, do, W)
+    ex["dq"] = orc.dense_rope(ex["dq"], cos, sin, inverse=True)
+    ex["dk"] = orc.dense_rope(ex["dk"], cos, sin, inverse=True)
+    return ex
+
+
 def test_window_of_one_key(cuda_device):
-    """W = 1 (two visible keys) on many rows: nothing averages the bf16 rounding of P and dS over keys,
-    so single elements of dQ / dK (|values| up to about 10) differ from the fp32 oracle by up to one
-    half ulp of bf16 of the largest term, about 2.5e-2; the relative L2 error stays at 4e-3.  The
-    absolute bound is therefore 3e-2 here, the relative one unchanged."""
+    """W = 1 (two visible keys) on every row: nothing averages a rounding over keys.  The rotated
+    q, k enter the tensor cores as bf16 while the oracle keeps them in fp32, and with two keys per
+    row that operand rounding alone - exact arithmetic on the rounded operands - already puts
+    single elements of dQ, dK (|values| up to 5) 1.8e-2 from the oracle.  The kernels' own
+    arithmetic must stay within 1e-2 of the exact result on their operands (they carry dS as two
+    bf16 terms here and round P rather than truncate it); against the oracle the bound for this
+    regime is 2.5e-2, the relative one unchanged."""
     import torch
     for B, T, H in ((6, 127, 3), (12, 1400, 1)):
-        got, want = run_path(B, T, H, 1, True, torch.bfloat16)
-        assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), max_abs=3e-2, what=f"W=1 B{B} T{T} H{H}")
+        (cos, sin), _ = rope_tables(T)
+        exact = None
+        for flow in ("fused", "saved"):
+            got, want = run_path(B, T, H, 1, True, torch.bfloat16, flow=flow)
+            rep = compare(got, want, ["o", "lse", "dq", "dk", "dv"])
+            assert_parity(rep, max_abs=2.5e-2, what=f"W=1 B{B} T{T} H{H} {flow}")
+            if exact is None:
+                host, _ = device_inputs(B, T, H, seed=3)
+                exact = _exact_on_kernel_operands(host, cos, sin, 1)
+                floor = {n: orc.parity(exact[n], want[n])[0] for n in ("dq", "dk")}
+                print(f"W=1 B{B} T{T} H{H}: operand rounding alone: {floor}; kernels vs oracle: "
+                      f"{ {n: round(v[0], 4) for n, v in rep.items()} }")
+            assert_parity(compare(got, exact, ["dq", "dk", "dv"]), max_abs=1e-2, what=f"W=1 vs exact on operands {flow}")
 
 
 def _random_cases(seed, n):
@@ -84,13 +140,11 @@ def _random_cases(seed, n):
 @pytest.mark.parametrize("B,T,H,W,rope", _random_cases(2024, 14))
 def test_random_shapes(cuda_device, B, T, H, W, rope):
     """Seeded sweep over sequence lengths around the tile sizes, unit counts on both sides of the SM
-    count and windows on both sides of the tile size.  Over many units the largest single-element
-    error of dQ / dK passes 2e-2 now and then (the rows of a causal sequence that see one or two keys:
-    nothing averages the bf16 rounding of dS there), hence 3e-2 here; the relative bound is unchanged."""
+    count and windows on both sides of the tile size, at the ordinary bounds; the RoPE flow
+    alternates with the shape."""
     import torch
-    got, want = run_path(B, T, H, W, rope, torch.bfloat16, seed=1000 + T)
-    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), max_abs=3e-2,
-                  what=f"B{B} T{T} H{H} W{W} rope{rope}")
+    got, want = run_path(B, T, H, W, rope, torch.bfloat16, seed=1000 + T, flow=FLOWS[(B + T + H) % 3])
+    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"B{B} T{T} H{H} W{W} rope{rope}")
 
 
 def test_config1_fp32_io(cuda_device):
@@ -101,21 +155,57 @@ def test_config1_fp32_io(cuda_device):
     assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what="config 1")
 
 
-def test_config2_one_unit_per_window(cuda_device):
+@pytest.mark.parametrize("flow", FLOWS)
+def test_config2_one_unit_per_window(cuda_device, flow):
     """BASELINE config 2 shape per (b,h) unit: T=2048, W=1024 and W=2048 (SSSL), bf16."""
     import torch
     for W in (1024, 2048):
-        got, want = run_path(1, 2048, 2, W, True, torch.bfloat16, seed=1)
-        assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"config 2 W={W}")
+        got, want = run_path(1, 2048, 2, W, True, torch.bfloat16, seed=1, flow=flow)
+        assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"config 2 W={W} {flow}")
 
 
+@pytest.mark.parametrize("flow", ["fused", "saved"])
 @pytest.mark.parametrize("W", [1024, 0])
-def test_config4_long_context_unit(cuda_device, W):
+def test_config4_long_context_unit(cuda_device, W, flow):
     """BASELINE config 4 shape per unit: T=8192, head_dim 128, bf16, window 1024 and full causal
     (the rope table is extended past the reference's 2048 rows with the same formula)."""
     import torch
-    got, want = run_path(1, 8192, 1, W, True, torch.bfloat16, seed=4)
-    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"config 4 W={W}")
+    got, want = run_path(1, 8192, 1, W, True, torch.bfloat16, seed=4, flow=flow)
+    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), what=f"config 4 W={W} {flow}")
+
+
+def _full_size_sampled(B, H, T, W, units, seed):
+    """Runs the benchmarked flow (saved rotated q, k; fp32 gradients) at full size on tensors drawn on
+    the device, and compares the (b, h) units listed in `units` with the oracle run on exactly
+    those units' operands."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q, k, v, do = (torch.randn(B, T, H, 128, device="cuda", generator=g).to(torch.bfloat16) for _ in range(4))
+    (cos, sin), dtab = rope_tables(T)
+    p = ab.AttnParams(window=W, rope=dtab, q_rot=torch.empty_like(q), k_rot=torch.empty_like(k))
+    o, lse = ab.attn_fwd(q, k, v, p)
+    dq, dk, dv, _ = ab.attn_bwd(q, k, v, o, do, lse, p)
+    _device_ok()
+    for b, h in units:
+        sl = (slice(b, b + 1), slice(None), slice(h, h + 1))
+        host = [t[sl].float().cpu().numpy() for t in (q, k, v, do)]
+        want = orc.attention_path(*host[:3], host[3], W, rope=(cos, sin))
+        got = {n: t[sl] for n, t in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv))}
+        assert_parity(compare(got, want), what=f"B{B} H{H} T{T} W{W} unit ({b},{h})")
+
+
+@pytest.mark.parametrize("W", [1024, 2048])
+def test_config2_full_size_sampled_units(cuda_device, W):
+    """BASELINE config 2 at full size (B=16, H=4, T=2048) in the flow bench.py times.  The persistent
+    kernels deal their work items out in rounds of one per SM, ordered by query / key tile and then by
+    unit index b*H + h, so units from the start, the middle and the end of the unit range put their
+    items at the start, the middle and the end of every round (and on different SMs)."""
+    _full_size_sampled(16, 4, 2048, W, [(0, 0), (5, 1), (8, 2), (10, 3), (15, 3)], seed=20 + W)
+
+
+def test_config5_per_gpu_size_sampled_units(cuda_device):
+    """BASELINE config 5 as one of eight GPUs sees it (B=16 of 128, H=8, T=2048, W=1024)."""
+    _full_size_sampled(16, 8, 2048, 1024, [(0, 0), (3, 5), (8, 2), (12, 7), (15, 7)], seed=55)
 
 
 def test_config5_shape_sharded_like_two_ranks(cuda_device):
@@ -148,8 +238,12 @@ def test_config5_shape_sharded_like_two_ranks(cuda_device):
 def test_rope_prepass_and_bf16_grads(cuda_device):
     import torch
     got, want = run_path(2, 520, 2, 200, True, torch.bfloat16, grad_dtype=torch.bfloat16, prepass=True)
-    # bf16 gradient outputs add half an ulp of bf16 (2^-9 relative) on top of the compute error
-    assert_parity(compare(got, want, ["o", "lse", "dq", "dk", "dv"]), max_abs=4e-2, what="bf16 grads")
+    assert_parity(compare(got, want, ["o", "lse"]), what="bf16 grads: o, lse")
+    # Storing a gradient as bf16 rounds it once more: half an ulp, 2^-9 of its magnitude, on top of
+    # the compute error.  The absolute bound for these outputs is therefore 2e-2 + 2^-9 max|want|.
+    for n in ("dq", "dk", "dv"):
+        bound = MAX_ABS_TOL + float(np.abs(want[n]).max()) / 512.0
+        assert_parity(compare(got, want, [n]), max_abs=bound, what=f"bf16 grads: {n}")
 
 
 @pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])

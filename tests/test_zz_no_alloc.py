@@ -37,13 +37,27 @@ def test_noalloc_forward_matches_allocating_entry_point_twice(cuda_device):
         lse_ref = torch.empty(B, T, H, device="cuda")
         lse_new = torch.full((B, T, H), float("nan"), device="cuda")
         _call(L.ar_flash_attn_fwd, o_ref, lse_ref, q, k, v, B, T, H, W)
+        torch.cuda.synchronize()
+        # The property the entry point exists for: the call must not take device memory.  Free
+        # bytes are read straight from the driver before and after (the first call on a device
+        # only looks a symbol address up, which allocates nothing either).
+        free_before = torch.cuda.mem_get_info()[0]
         _call(L.ar_flash_attn_fwd_noalloc, o_new, lse_new, q, k, v, B, T, H, W)
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, (call, "device memory was allocated")
+        assert L.ar_noalloc_status() == _lib.AR_OK, L.ar_last_error()
+        assert torch.cuda.mem_get_info()[0] == free_before, (call, "status read allocated device memory")
         for name, got, want in (("o", o_new, o_ref), ("lse", lse_new, lse_ref)):
             max_abs, rel = orc.parity(got.cpu().numpy(), want.cpu().numpy())
             assert max_abs <= MAX_ABS_TOL and rel <= REL_L2_TOL, (call, name, max_abs, rel)
             # same kernels on the same staged operands: in practice the results are identical
             assert torch.equal(got, want), (call, name)
+        # and against the CPU oracle on the operands the kernels see (q, k, v rounded to bf16)
+        host = [orc.to_bf16_rne(t.cpu().numpy()) for t in (q, k, v)]
+        want = orc.attention_path(*host, None, W)
+        for name, got in (("o", o_new), ("lse", lse_new)):
+            max_abs, rel = orc.parity(got.cpu().numpy(), want[name])
+            assert max_abs <= MAX_ABS_TOL and rel <= REL_L2_TOL, (call, name, "oracle", max_abs, rel)
 
 
 def test_noalloc_rejects_sizes_beyond_its_fixed_scratch(cuda_device):
