@@ -28,15 +28,13 @@
 // residual, the latter in the 16 columns of G2 each warpgroup has left over - and P^T is rounded
 // instead of truncated: such a key has nothing to average a bf16 rounding over, and with |dK| near
 // 10 one rounding of dS (2^-9 relative) would be the whole error budget.
-// Thread r of a compute warpgroup owns TMEM lane r (one key).  The write-out of an item belongs to
-// a warpgroup of its own (warps 12-15), so that the compute warpgroups start the next item's
-// sub-tiles at once: it reads the accumulators 32 columns at a time (dV first, then dK, each
-// released to the next item's accumulation as soon as its last columns have been read), multiplies
-// dK by 1/sqrt(D) (ops.mojo:479), applies the inverse rotation of rope_bwd when asked, and writes
-// full 128-byte lines with plain stores through a per-warp transposition buffer - nothing the CTA
-// has to wait for, unlike a bulk store.  The 128 KB of fp32 gradients of an item take about 4.5k
-// cycles at the rate an SM retires stores; only what of that outlasts the next item's first two
-// sub-tiles (whose products need no accumulator) still holds the tensor pipe up.
+// Thread r of a compute warpgroup owns TMEM lane r (one key).  At the end of an item the compute
+// threads pull their accumulator rows into registers (which frees tensor memory for the next
+// item's accumulation), multiply dK by 1/sqrt(D) (ops.mojo:479), apply the inverse rotation of
+// rope_bwd when asked, and write the rows out through a small per-warp transposition buffer with
+// plain coalesced stores - nothing the CTA has to wait for, unlike a bulk store.
+#include <type_traits>
+
 #include "attn_common.cuh"
 
 namespace ar {
@@ -45,20 +43,19 @@ constexpr int kSub = 64;                      // rows of a streamed sub-tile
 constexpr int kSubBytes = kSub * 128 * 2;     // 16 KB: two 8 KB boxes (d 0..63, d 64..127)
 constexpr int kSubHalf = kSub * 64 * 2;       // 8 KB
 constexpr int kBwdStages = 4;
-constexpr int kBwdThreads = 512;  // warps 0-3, 4-7 compute; 8 TMA; 9, 10 MMA issuers; 11 idle; 12-15 write-out
-constexpr int kWarpStore0 = 12;
-constexpr int kEpiBytes = 4096;   // per write-out warp: two blocks of 16 rows x 128 bytes
+constexpr int kBwdThreads = 384;  // warps 0-3, 4-7 compute; 8 TMA; 9, 10 MMA issuers; 11 idle
+constexpr int kEpiBytes = 2048;   // per compute warp: 32 rows x 64 bytes
 
 struct BwdSmem {
   alignas(1024) uint8_t x1[kTileBytes];             // K
   alignas(1024) uint8_t x2[kTileBytes];             // V
   alignas(1024) uint8_t y1[kBwdStages][kSubBytes];  // Q sub-tiles
   alignas(1024) uint8_t y2[kBwdStages][kSubBytes];  // dO sub-tiles
-  alignas(1024) uint8_t epi[4][kEpiBytes];          // write-out transposition buffers
+  alignas(1024) uint8_t epi[8][kEpiBytes];          // write-out transposition buffers
   alignas(128) float stats[kBwdStages][2][kSub];    // per stage: exponent addend and D of its 64 queries
   alignas(8) uint64_t x_full, x_free;
   uint64_t y_full[kBwdStages], y_empty[kBwdStages];
-  uint64_t g_full[2], ready[2], acc_done, acc_free[2];   // acc_free: dV, dK
+  uint64_t g_full[2], ready[2], acc_done, acc_free;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -92,9 +89,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
   grid_dep_launch_dependents();   // all CTAs of this grid are resident: the next kernel may be scheduled
   WaitCtx w{p.status, smem_u32(&sm.abort_flag)};
-#ifdef AR_TRACE
-  const bool trace_on = blockIdx.x == 5 && lane == 0 && (warp == 0 || warp == 4 || warp == 9 || warp == 10);
-#endif
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&sm.x_full), 1);
     mbar_init(smem_u32(&sm.x_free), 2);        // both issuers have issued the item's last product
@@ -107,9 +101,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       mbar_init(smem_u32(&sm.ready[i]), 256);
     }
     mbar_init(smem_u32(&sm.acc_done), 2);      // both accumulations of the item are complete
-    mbar_init(smem_u32(&sm.acc_free[0]), 4);   // the four write-out warps have read dV ...
-    mbar_init(smem_u32(&sm.acc_free[1]), 4);   // ... dK
-    sm.abort_flag = (*p.status != 0u) ? 1u : 0u;   // an earlier abandoned wait: do no work
+    mbar_init(smem_u32(&sm.acc_free), 256);    // every compute thread holds its accumulator row
+    sm.abort_flag = 0u;
     fence_mbar_init();
     prefetch_tmap(&map_k);
     prefetch_tmap(&map_v);
@@ -124,59 +117,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   __syncthreads();
   tc_fence_after();
   grid_dep_wait();   // everything above overlapped the previous kernel's tail; its results are visible from here
+  // An earlier abandoned wait (this or a previous kernel's, status word still set): do no work.  The
+  // word is read only now, when the previous kernel's writes are visible.  Without data from the TMA
+  // warp no hand-shake of this CTA can complete, so it is enough that the producers stay idle: every
+  // other role gives up at its first wait.
+  if (threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) sm.abort_flag = 1u;
+  __syncthreads();
+  const bool live = ld_shared_u32(smem_u32(&sm.abort_flag)) == 0u;
   const uint32_t tmem = sm.tmem_base;
   constexpr uint32_t kColAcc0 = 0, kColAcc1 = 128, kColBuf = 256;
   // Queries y0 .. y0+63 against the keys row0 .. row0+127: can the sub-tile hold the queries of a key
   // that fewer than 16 queries see in all?  Those are the last 15 keys of a sequence (in the last key
   // tile) and, under a window below 15, every key (its queries lie in the sub-tiles a mask edge crosses).
+  auto two_term_item = [&](int row0) { return (window > 0 && window < 15) || row0 + kTile >= T; };
   auto edge_sub = [&](int y0, int row0) {
     if (window > 0 && window < 15) return y0 < row0 + kTile - 1 || y0 + kSub - 1 > row0 + window;
     return row0 + kTile >= T;
   };
 
-  if (warp >= kWarpStore0) {
-    // ------------------------------------------------------------------ write-out warps
-    setmaxnreg_dec<56>();
-    const int wq = warp - kWarpStore0;
-    const uint32_t lane_off = static_cast<uint32_t>(wq * 32) << 16;
-    const uint32_t epi = smem_u32(sm.epi[wq]);
-    const int esize = p.grad_f32 ? 4 : 2;
-    const size_t row_stride = (size_t)H * 128 * esize;
-    int n = 0;
-    bool ok = true;
-    for (int k = 0; ok; ++k) {
-      const int item = sched_item(k, n_items);
-      if (item == -1) break;
-      if (item == -2) continue;
-      const DkvItem wi = dkv_item(item, p.dims);
-      if (!mbar_wait(w, smem_u32(&sm.acc_done), n & 1)) break;
-      tc_fence_after();
-      const int wrow0 = wi.row0 + 32 * wq;   // first row of this warp's 32-row block
-      const int rows_valid = T - wrow0;
-#pragma unroll 1
-      for (int a = 0; a < 2; ++a) {           // dV, then dK
-        const uint32_t acc = tmem + lane_off + (a == 0 ? kColAcc0 : kColAcc1);
-        uint8_t* gout = static_cast<uint8_t*>(a == 0 ? p.dv : p.dk) + (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
-        const float mul = a == 0 ? 1.f : p.scale * kTruncGainInv;   // dS carried the gain of P'
-        const bool rot = a == 1 && p.cos_buf != nullptr;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {         // column blocks [32c, 32c+32) and [64+32c, 64+32c+32): a rotation pair
-          store_block_pair(epi, lane, acc + 32 * c, acc + 64 + 32 * c, mul, gout + (size_t)(32 * c) * esize,
-                           gout + (size_t)(64 + 32 * c) * esize, row_stride, rows_valid, p.grad_f32,
-                           rot ? p.cos_buf + 32 * c : nullptr, rot ? p.sin_buf + 32 * c : nullptr, wrow0, T,
-                           c == 1 ? smem_u32(&sm.acc_free[a]) : 0u);
-        }
-      }
-      ++n;
-    }
-  } else if (warp >= 8) {
+  if (warp >= 8) {
   // One setmaxnreg instruction per warpgroup: the compute warpgroups take the registers the
-  // data-movement and write-out warpgroups give up.
-  setmaxnreg_dec<40>();
+  // data-movement warpgroup gives up.
+  setmaxnreg_dec<88>();
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     int g = 0, n = 0;   // sub-tiles and items issued so far: ring stage and barrier phases follow them
-    bool ok = true;
+    bool ok = live;
     for (int k = 0; ok; ++k) {
       const int item = sched_item(k, n_items);
       if (item == -1) break;
@@ -231,9 +197,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       const int s = gg % kBwdStages, bf = gg & 1;
       if (!mbar_wait(w, smem_u32(&sm.ready[bf]), (gg >> 1) & 1)) return false;
       // the item's first accumulation overwrites dV / dK: the previous item's rows must have left
-      if (it == 0 && n > 0 && !mbar_wait(w, smem_u32(&sm.acc_free[I]), (n - 1) & 1)) return false;
+      if (it == 0 && n > 0 && !mbar_wait(w, smem_u32(&sm.acc_free), (n - 1) & 1)) return false;
       tc_fence_after();
-      TRACE(2 + I, gg, 2);
       const uint32_t a_tmem = tmem + kColBuf + bf * 128 + I * 64;   // P in G1, dS in G2
       const uint32_t yb = smem_u32(I == 0 ? sm.y2[s] : sm.y1[s]);
 #pragma unroll
@@ -247,7 +212,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         make_sdesc_sw128(yb + ks * 2048, kSubHalf, 1024), idesc_acc, 1u);
       }
       umma_commit_elect(smem_u32(&sm.y_empty[s]));
-      TRACE(2 + I, gg, 3);
       return true;
     };
 
@@ -261,7 +225,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const int gg = g0 + it, s = gg % kBwdStages, bf = gg & 1;
         if (!mbar_wait(w, smem_u32(&sm.y_full[s]), (gg / kBwdStages) & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(2 + I, gg, 0);
         const uint32_t ya = smem_u32(I == 0 ? sm.y1[s] : sm.y2[s]);
         const uint32_t g_tmem = tmem + kColBuf + bf * 128 + I * 64;
 #pragma unroll
@@ -270,7 +233,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         make_sdesc_sw128(ya + (ks >> 2) * kSubHalf + (ks & 3) * 32, 0, 1024), idesc_g, ks > 0);
         umma_commit_elect(smem_u32(&sm.g_full[bf]));
         if (it == wi.n_sub - 1) umma_commit_elect(smem_u32(&sm.x_free));   // last read of K / V
-        TRACE(2 + I, gg, 1);
         if (it > 0 && !accumulate(it - 1, gg - 1, edge_sub((wi.hlo + it - 1) * kSub, wi.row0))) { ok = false; break; }
       }
       if (!ok || !accumulate(wi.n_sub - 1, g0 + wi.n_sub - 1, edge_sub((wi.hlo + wi.n_sub - 1) * kSub, wi.row0))) { ok = false; break; }
@@ -285,6 +247,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int wg = warp >> 2;                 // handles columns [32 wg, 32 wg + 32) of every sub-tile
     const int r = threadIdx.x & 127;          // TMEM lane = key row of the tile
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t epi = smem_u32(sm.epi[warp]);
     const f32x2 sc2 = f2_pack(p.scale_log2e, p.scale_log2e);
     int g0 = 0, n = 0;
     bool ok = true;
@@ -294,7 +257,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       if (item == -2) continue;
       const DkvItem wi = dkv_item(item, p.dims);
       const int row0 = wi.row0, row = row0 + r;
-      TRACE(wg, 56 + (n & 3), 0);
+      // The loop over the item's sub-tiles exists in two copies, chosen once per item: only the rare
+      // items that can hold two-term sub-tiles (see the head of the file) pay for the second pass.
+      auto sub_loop = [&](auto may_two) {
+      constexpr bool kMayTwo = decltype(may_two)::value;
       for (int it = 0; it < wi.n_sub; ++it) {
         const int gg = g0 + it, bf = gg & 1, s = gg % kBwdStages;
         // The per-query statistics of this stage arrived with its tiles (same mbarrier), before the
@@ -310,7 +276,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         if (!mbar_wait(w, smem_u32(&sm.g_full[bf]), (gg >> 1) & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(wg, gg, 0);
         const int ybase = (wi.hlo + it) * kSub + wg * 32;   // first query of this thread's 32 columns
         const uint32_t buf = tmem + lane_off + kColBuf + bf * 128 + wg * 32;
         // row = key, column = query: visible iff q >= key and (no window or q <= key + window)
@@ -319,7 +284,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         const int hi = window > 0 ? row + window - ybase : (1 << 30);
         uint32_t sr[32], dr[32];
         tmem_ld32x2_wait(buf, sr, buf + 64, dr);
-        TRACE(wg, gg, 1);
         // Masking is a separate, rarely taken pass so that the main loop stays branch-free.  The
         // rows of a warp are consecutive: when lane 31 sees the chunk from its first column (lane 0
         // up to its last) the whole warp does, and that edge needs no per-element test.
@@ -362,13 +326,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             f2_unpack(f2_mul(f2_pack(p0, p1), f2_sub(f2_pack_u(dr[j], dr[j + 1]), dd[e])), s0, s1);
             pp[2 * i + e] = pack_bf16x2_trunc(p0, p1);
             pd[2 * i + e] = pack_bf16x2_alu(s0, s1);
-            sr[j] = __float_as_uint(p0);       // kept for the second pass of an edge sub-tile
-            sr[j + 1] = __float_as_uint(p1);
-            dr[j] = __float_as_uint(s0);
-            dr[j + 1] = __float_as_uint(s1);
+            if (kMayTwo) {   // kept for the second pass of a two-term sub-tile
+              sr[j] = __float_as_uint(p0);
+              sr[j + 1] = __float_as_uint(p1);
+              dr[j] = __float_as_uint(s0);
+              dr[j + 1] = __float_as_uint(s1);
+            }
           }
         }
-        const bool two_terms = edge_sub((wi.hlo + it) * kSub, row0);   // CTA-uniform
+        const bool two_terms = kMayTwo && edge_sub((wi.hlo + it) * kSub, row0);   // CTA-uniform
         uint32_t pl[16];
         if (two_terms) {
 #pragma unroll
@@ -383,16 +349,57 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         tmem_st16(buf, pp);        // P^T feeds dV
         tmem_st16(buf + 64, pd);   // dS^T feeds dK
         if (two_terms) tmem_st16(buf + 64 + 16, pl);
-        TRACE(wg, gg, 2);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.ready[bf]));
-        TRACE(wg, gg, 3);
       }
+      };
+      if (two_term_item(row0)) sub_loop(std::true_type{});
+      else sub_loop(std::false_type{});
       if (!ok) break;
       g0 += wi.n_sub;
-      TRACE(wg, 56 + (n & 3), 1);
-      TRACE(wg, 56 + (n & 3), 3);
+      if (!mbar_wait(w, smem_u32(&sm.acc_done), n & 1)) { ok = false; break; }
+      tc_fence_after();
+      // Warpgroup 0 writes out dV, warpgroup 1 dK (scaled, rotated back).  The accumulator row goes
+      // to registers first, which frees tensor memory for the next item's accumulation.
+      const uint32_t acc = tmem + lane_off + (wg == 0 ? kColAcc0 : kColAcc1);
+      uint32_t a0[32], a1[32], b0[32], b1[32];   // columns [0,32) [32,64) | [64,96) [96,128)
+      tmem_ld32x2_wait(acc, a0, acc + 32, a1);
+      tmem_ld32x2_wait(acc + 64, b0, acc + 96, b1);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sm.acc_free));
+      const int esize = p.grad_f32 ? 4 : 2;
+      const size_t row_stride = (size_t)H * 128 * esize;
+      const int wrow0 = row0 + 32 * (warp & 3);   // first row of this warp's 32-row block
+      uint8_t* gout = static_cast<uint8_t*>(wg == 0 ? p.dv : p.dk) +
+                      (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
+      const int rows_valid = T - wrow0;
+      const float mul = wg == 0 ? 1.f : p.scale * kTruncGainInv;   // dS carried the gain of P'
+      const bool rot = wg == 1 && p.cos_buf != nullptr;
+      const int pos = min(row, T - 1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float lo_v[32], hi_v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          lo_v[i] = __uint_as_float(c == 0 ? a0[i] : a1[i]) * mul;
+          hi_v[i] = __uint_as_float(c == 0 ? b0[i] : b1[i]) * mul;
+        }
+        if (rot) {
+          const float4* cp = reinterpret_cast<const float4*>(p.cos_buf + (size_t)pos * 64 + c * 32);
+          const float4* sp = reinterpret_cast<const float4*>(p.sin_buf + (size_t)pos * 64 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
+            rope_bwd_pair(lo_v[4 * i], hi_v[4 * i], cv.x, sv.x);
+            rope_bwd_pair(lo_v[4 * i + 1], hi_v[4 * i + 1], cv.y, sv.y);
+            rope_bwd_pair(lo_v[4 * i + 2], hi_v[4 * i + 2], cv.z, sv.z);
+            rope_bwd_pair(lo_v[4 * i + 3], hi_v[4 * i + 3], cv.w, sv.w);
+          }
+        }
+        warp_store_32cols(epi, lane, lo_v, gout + (size_t)(c * 32) * esize, row_stride, rows_valid, p.grad_f32);
+        warp_store_32cols(epi, lane, hi_v, gout + (size_t)(64 + c * 32) * esize, row_stride, rows_valid, p.grad_f32);
+      }
       ++n;
     }
   }
@@ -421,6 +428,5 @@ cudaError_t launch_attn_bwd_dkv(const CUtensorMap& mq, const CUtensorMap& mk, co
   return launch_pdl(attn_bwd_dkv_kernel, grid, kBwdThreads, smem, stream, mk, mv, mq, mdo, p, n_items);
 }
 
-AR_TRACE_READER(ar_debug_bwd_trace)
 
 }  // namespace ar

@@ -24,17 +24,18 @@
 // residual, each through its own dQ product: such a query has nothing to average the bf16 rounding
 // of dS over, and with |dQ| near 10 a single rounding (2^-9 relative) would already be the whole
 // error budget.  Everywhere else (at least 16 visible keys per row) one term is carried.
-// When asked (bf16 tensors, D and dQ both wanted) four more warps compute
+// When asked (bf16 tensors, D and dQ both wanted) four otherwise idle warps compute
 // D = rowsum(O * dO) for the queries of the item after the one in flight, replacing
 // flash_attn_bwd_precompute_d (ops.mojo:329-346) and the key-stationary re-layout the dK/dV
 // kernel needs.
-// The write-out of an item belongs to the same four warps (after the D of the item ahead), so that
-// the compute warpgroups start the next item's tiles at once: they read the dQ accumulator 32
-// columns at a time (releasing it to the next item as soon as its last columns have been read),
-// multiply by 1/sqrt(D) (ops.mojo:411), apply the inverse rotation of rope_bwd when asked, and
-// write full 128-byte lines with plain stores through per-warp transposition buffers.  Those live
-// in the V-ring slot that held the item's last V tile: the next item needs that slot only for its
-// second V tile, and the TMA warp holds that one load back until the write-out is done.
+// At the end of an item warpgroups 0 and 1 pull the dQ rows into registers (which frees the
+// accumulator for the next item), multiply by 1/sqrt(D) (ops.mojo:411), apply the inverse rotation
+// of rope_bwd when asked, and write the rows out with plain coalesced stores through per-warp
+// transposition buffers.  Those live in the V-ring slot that held the item's last V tile: the next
+// item needs that slot only for its second V tile, and the TMA warp holds that one load back until
+// the write-out is done.
+#include <type_traits>
+
 #include "attn_common.cuh"
 
 namespace ar {
@@ -89,9 +90,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   grid_dep_launch_dependents();   // all CTAs of this grid are resident: the next kernel may be scheduled
   WaitCtx w{p.status, smem_u32(&sm.abort_flag)};
-#ifdef AR_TRACE
-  const bool trace_on = blockIdx.x == 5 && lane == 0 && (warp == 0 || warp == kDqCW + 1 || warp == kDqCW + 2 || warp == kDqCW + 3);
-#endif
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&sm.x_full), 1);
     mbar_init(smem_u32(&sm.x_free), 2);      // the S and the dP issuer have issued the item's last product
@@ -114,9 +112,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     mbar_init(smem_u32(&sm.ready), kDqCW * 32);   // dS written
     mbar_init(smem_u32(&sm.ds_free), 1);     // dQ MMAs of the tile have consumed dS
     mbar_init(smem_u32(&sm.acc_done), 1);
-    mbar_init(smem_u32(&sm.acc_free), 4);    // the four write-out warps have read the dQ rows
-    mbar_init(smem_u32(&sm.epi_free), 4);    // ... and are done with their transposition buffers
-    sm.abort_flag = (*p.status != 0u) ? 1u : 0u;   // an earlier abandoned wait: do no work
+    mbar_init(smem_u32(&sm.acc_free), 8);    // the eight write-out warps hold their dQ rows
+    mbar_init(smem_u32(&sm.epi_free), 8);    // ... and have read their transposition buffers
+    sm.abort_flag = 0u;
     fence_mbar_init();
     prefetch_tmap(&map_q);
     prefetch_tmap(&map_do);
@@ -131,6 +129,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   tc_fence_after();
   grid_dep_wait();   // everything above overlapped the previous kernel's tail; its results are visible from here
+  // An earlier abandoned wait (this or a previous kernel's, status word still set): do no work.  The
+  // word is read only now, when the previous kernel's writes are visible.  Without data from the TMA
+  // warp no hand-shake of this CTA can complete, so it is enough that the producers stay idle: every
+  // other role gives up at its first wait.
+  if (threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) sm.abort_flag = 1u;
+  __syncthreads();
+  const bool live = ld_shared_u32(smem_u32(&sm.abort_flag)) == 0u;
   const uint32_t tmem = sm.tmem_base;
   constexpr uint32_t kColDQ = 0, kColS = 128, kColDP = 256, kColDS = 384, kColDSLo = 448;
   // Tile kb .. kb+127 against the queries row0 .. row0+127: can it hold the keys of a query that sees
@@ -142,112 +147,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     return row0 == 0 && kb == 0;
   };
 
-  if (warp >= kDqCW + 4) {
-    // ------------------------------------------------------------------ D and write-out warps
-    setmaxnreg_dec<56>();
-    const int wq = warp - (kDqCW + 4);             // rows [32 wq, 32 wq + 32) of the tile
-    const uint32_t lane_off = static_cast<uint32_t>(wq * 32) << 16;
-    const bool fuse_d = p.o_for_d != nullptr;
-    const int esize = p.grad_f32 ? 4 : 2;
-    const size_t row_stride = (size_t)H * 128 * esize;
-    // write-out of item `ns` (the ns-th of this CTA), whose tiles end at global tile count g_end
-    auto write_out = [&](const DqItem& wi, int ns, int g_end) -> bool {
-      if (!mbar_wait(w, smem_u32(&sm.acc_done), ns & 1)) return false;
-      tc_fence_after();
-      // transposition buffer of this warp: 4 KB of the V slot that held the item's last V tile
-      const uint32_t epi = smem_u32(sm.v[(g_end - 1) % kDqVStages]) + wq * 4096u;
-      const int wrow0 = wi.row0 + 32 * wq;
-      uint8_t* gout = static_cast<uint8_t*>(p.dq) + (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
-      const uint32_t acc = tmem + lane_off + kColDQ;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c)   // column blocks [32c, 32c+32) and [64+32c, 64+32c+32): a rotation pair
-        store_block_pair(epi, lane, acc + 32 * c, acc + 64 + 32 * c, p.scale * kTruncGainInv,   // dS carried the gain of P'
-                         gout + (size_t)(32 * c) * esize, gout + (size_t)(64 + 32 * c) * esize, row_stride, T - wrow0,
-                         p.grad_f32, p.cos_buf ? p.cos_buf + 32 * c : nullptr, p.cos_buf ? p.sin_buf + 32 * c : nullptr,
-                         wrow0, T, c == 1 ? smem_u32(&sm.acc_free) : 0u);
-      fence_proxy_async_smem();   // the slot is next written by a bulk tensor load
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.epi_free));
-      return true;
-    };
-    const int half = lane >> 4, ch = lane & 15;
-    int n = 0, g = 0, g_prev = 0;
-    DqItem prev = {};
-    bool ok = true;
-    for (int k = 0; ok; ++k) {
-      const int item = sched_item(k, n_items);
-      if (item == -1) break;
-      if (item == -2) continue;
-      const DqItem di = dq_item(item, p.dims, n_qt);
-      if (fuse_d) {
-      // D[row] = sum_d O[row,d] * dO[row,d] (ops.mojo:329-346) for this item's 128 queries, an item
-      // ahead of the compute warps and off their critical path.  Each instruction reads two complete
-      // 256-byte rows (16 lanes x 16 bytes) from global memory (dO is in L2: the TMA warp streams the
-      // same tile); the 16 partial sums of a row meet by shuffles.  D goes to shared memory for the
-      // compute threads, to d_out, and with the exponent addend to the key-stationary arrays that
-      // the dK/dV kernel streams.
-      float mine = 0.f;   // D of row 32 wq + lane
-#pragma unroll 1
-      for (int bt = 0; bt < 4; ++bt) {
-        uint4 ov[4], dv[4];
-#pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-          const int row_g = di.row0 + 32 * wq + 8 * bt + 2 * pp + half;
-          if (row_g < T) {
-            const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
-            ov[pp] = __ldg(reinterpret_cast<const uint4*>(p.o_for_d + ri * 128) + ch);
-            dv[pp] = __ldg(reinterpret_cast<const uint4*>(p.do_for_d + ri * 128) + ch);
-          } else {
-            ov[pp] = make_uint4(0, 0, 0, 0);
-            dv[pp] = make_uint4(0, 0, 0, 0);
-          }
-        }
-#pragma unroll
-        for (int pp = 0; pp < 4; ++pp) {
-          const uint32_t ow[4] = {ov[pp].x, ov[pp].y, ov[pp].z, ov[pp].w}, dw[4] = {dv[pp].x, dv[pp].y, dv[pp].z, dv[pp].w};
-          float acc = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            acc += bf16_lo_to_f32(ow[i]) * bf16_lo_to_f32(dw[i]) + bf16_hi_to_f32(ow[i]) * bf16_hi_to_f32(dw[i]);
-#pragma unroll
-          for (int off = 8; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-          // lanes 0..15 hold the sum of row 8 bt + 2 pp, lanes 16..31 that of the next row
-          const float lo_row = __shfl_sync(0xffffffffu, acc, 0), hi_row = __shfl_sync(0xffffffffu, acc, 16);
-          if (lane == 8 * bt + 2 * pp) mine = lo_row;
-          if (lane == 8 * bt + 2 * pp + 1) mine = hi_row;
-        }
-      }
-      const int row_l = 32 * wq + lane, row_g = di.row0 + row_l;
-      const bool valid = row_g < T;
-      // the compute warps must have taken the D of the item before the previous one (same buffer;
-      // each buffer has its own barriers, so that a waiter is never two phases behind)
-      if (n > 1 && !mbar_wait(w, smem_u32(&sm.d_taken[n & 1]), ((n >> 1) - 1) & 1)) break;
-      sm.d_row[n & 1][row_l] = valid ? mine : 0.f;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm.d_ready[n & 1]));
-      if (row_g < p.t_pad) {
-        const size_t ti = ((size_t)di.b * H + di.h) * p.t_pad + row_g;
-        float addend = -INFINITY;
-        if (valid) {
-          const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
-          p.d_out[ri] = mine;
-          addend = kTruncGainLog2 - p.lse[ri] * kLog2e;
-        }
-        p.dvec_t_out[ti] = valid ? mine : 0.f;
-        p.lse2_t_out[ti] = addend;
-      }
-      }
-      // with this item's D on its way, write the previous item out (it completes about now)
-      if (n > 0 && !write_out(prev, n - 1, g_prev)) { ok = false; break; }
-      g += di.n_it;
-      prev = di;
-      g_prev = g;
-      ++n;
-    }
-    if (ok && n > 0) write_out(prev, n - 1, g_prev);
-  } else if (warp >= kDqCW) {
+  if (warp >= kDqCW) {
   // registers move from the data-movement / issuing warpgroups to the compute warpgroups
-  setmaxnreg_dec<40>();
+  setmaxnreg_dec<48>();
   if (warp == kDqCW) {
     // ------------------------------------------------------------------ TMA producer
     // 128-row tile at `rows` of one (b,h): four 64-row boxes (two d-halves x two row blocks)
@@ -260,7 +162,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     };
     int g = 0, n = 0;        // tiles and items issued so far: ring stages and barrier phases follow them
     int epi_item = -1, epi_slot = 0;   // write-out not yet waited for, and the V slot it stages in
-    bool ok = true;
+    bool ok = live;
     for (int k = 0; ok; ++k) {
       const int item = sched_item(k, n_items);
       if (item == -1) break;
@@ -323,7 +225,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // S / dP of the previous tile (of this or the previous item) must be in the compute threads' registers
         if (g > 0 && !mbar_wait(w, smem_u32(&sm.g_free), (g - 1) & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(1 + I, g, 0);
         const uint32_t ya = smem_u32(I == 0 ? sm.k[s] : sm.v[s]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -334,7 +235,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         umma_commit_elect(smem_u32(&sm.g_full));
         umma_commit_elect(I == 0 ? smem_u32(&sm.k_empty[s]) : smem_u32(&sm.v_empty[s]));
         if (it == wi.n_it - 1) umma_commit_elect(smem_u32(&sm.x_free));   // last read of Q / dO
-        TRACE(1 + I, g, 1);
       }
       ++n;
     }
@@ -355,7 +255,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // the item's first product overwrites dQ: the previous item's rows must have left
         if (it == 0 && n > 0 && !mbar_wait(w, smem_u32(&sm.acc_free), (n - 1) & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(3, g, 0);
         const uint32_t ka = smem_u32(sm.k[s]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -369,17 +268,85 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         umma_commit_elect(smem_u32(&sm.ds_free));
         umma_commit_elect(smem_u32(&sm.k_empty[s]));
-        TRACE(3, g, 1);
       }
       if (!ok) break;
       umma_commit_elect(smem_u32(&sm.acc_done));
+      ++n;
+    }
+  } else if (warp >= kDqCW + 4 && p.o_for_d != nullptr) {
+    // ------------------------------------------------------------------ D warps
+    // D[row] = sum_d O[row,d] * dO[row,d] (ops.mojo:329-346) for an item's 128 queries, one item
+    // ahead of the compute warps and off their critical path.  Each instruction reads two complete
+    // 256-byte rows (16 lanes x 16 bytes) from global memory (dO is in L2: the TMA warp streams the
+    // same tile); the 16 partial sums of a row meet by shuffles.  D goes to shared memory for the
+    // compute threads, to d_out, and with the exponent addend to the key-stationary arrays that
+    // the dK/dV kernel streams.
+    const int wq = warp - (kDqCW + 4);             // rows [32 wq, 32 wq + 32) of the tile
+    const int half = lane >> 4, ch = lane & 15;
+    int n = 0;
+    bool ok = live;   // these warps read and write global memory without waiting for anyone
+    for (int k = 0; ok; ++k) {
+      const int item = sched_item(k, n_items);
+      if (item == -1) break;
+      if (item == -2) continue;
+      const DqItem di = dq_item(item, p.dims, n_qt);
+      float mine = 0.f;   // D of row 32 wq + lane
+#pragma unroll 1
+      for (int bt = 0; bt < 4; ++bt) {
+        uint4 ov[4], dv[4];
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+          const int row_g = di.row0 + 32 * wq + 8 * bt + 2 * pp + half;
+          if (row_g < T) {
+            const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
+            ov[pp] = __ldg(reinterpret_cast<const uint4*>(p.o_for_d + ri * 128) + ch);
+            dv[pp] = __ldg(reinterpret_cast<const uint4*>(p.do_for_d + ri * 128) + ch);
+          } else {
+            ov[pp] = make_uint4(0, 0, 0, 0);
+            dv[pp] = make_uint4(0, 0, 0, 0);
+          }
+        }
+#pragma unroll
+        for (int pp = 0; pp < 4; ++pp) {
+          const uint32_t ow[4] = {ov[pp].x, ov[pp].y, ov[pp].z, ov[pp].w}, dw[4] = {dv[pp].x, dv[pp].y, dv[pp].z, dv[pp].w};
+          float acc = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            acc += bf16_lo_to_f32(ow[i]) * bf16_lo_to_f32(dw[i]) + bf16_hi_to_f32(ow[i]) * bf16_hi_to_f32(dw[i]);
+#pragma unroll
+          for (int off = 8; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+          // lanes 0..15 hold the sum of row 8 bt + 2 pp, lanes 16..31 that of the next row
+          const float lo_row = __shfl_sync(0xffffffffu, acc, 0), hi_row = __shfl_sync(0xffffffffu, acc, 16);
+          if (lane == 8 * bt + 2 * pp) mine = lo_row;
+          if (lane == 8 * bt + 2 * pp + 1) mine = hi_row;
+        }
+      }
+      const int row_l = 32 * wq + lane, row_g = di.row0 + row_l;
+      const bool valid = row_g < T;
+      // the compute warps must have taken the D of the item before the previous one (same buffer;
+      // each buffer has its own barriers, so that a waiter is never two phases behind)
+      if (n > 1 && !mbar_wait(w, smem_u32(&sm.d_taken[n & 1]), ((n >> 1) - 1) & 1)) break;
+      sm.d_row[n & 1][row_l] = valid ? mine : 0.f;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm.d_ready[n & 1]));
+      if (row_g < p.t_pad) {
+        const size_t ti = ((size_t)di.b * H + di.h) * p.t_pad + row_g;
+        float addend = -INFINITY;
+        if (valid) {
+          const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
+          p.d_out[ri] = mine;
+          addend = kTruncGainLog2 - p.lse[ri] * kLog2e;
+        }
+        p.dvec_t_out[ti] = valid ? mine : 0.f;
+        p.lse2_t_out[ti] = addend;
+      }
       ++n;
     }
   }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
     // setmaxnreg.inc blocks until the registers exist: the totals after re-allocation must not
-    // exceed what the CTA was launched with (768 x 80 = 512 x 96 + 128 x 40 + 128 x 56), or the kernel deadlocks.
+    // exceed what the CTA was launched with (768 x 80 = 512 x 96 + 256 x 48), or the kernel deadlocks.
     setmaxnreg_inc<96>();
     const int wg = warp >> 2;
     const int r = threadIdx.x & 127;
@@ -401,42 +368,51 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       float d_row = (!fuse_d && valid) ? p.dvec[row_index] : 0.f;
       const f32x2 nl2 = f2_pack(kTruncGainLog2 - lse2, kTruncGainLog2 - lse2);
       f32x2 dd2 = f2_pack(d_row, d_row);
-      TRACE(0, 56 + (n & 3), 0);
+      // The loop over the item's key tiles exists in two copies, chosen once per item: items that can
+      // hold two-term tiles (see the head of the file; they are rare) also form the rounding
+      // residual of dS, which costs registers the common copy should not pay for.
+      auto tile_loop = [&](auto may_two) {
+      constexpr bool kMayTwo = decltype(may_two)::value;
       for (int it = 0; it < wi.n_it; ++it, ++g) {
         const int ybase = (wi.jlo + it) * kTile + wg * kDqCols;   // first key of this warpgroup's columns
         if (!mbar_wait(w, smem_u32(&sm.g_full), g & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(0, g, 0);
-        // Tiles that carry dS as two terms (see the head of the file) are rare, so their extra work is
-        // a second pass that loads S and dP from tensor memory once more rather than a longer common
-        // path; S / dP are released to the next tile's products after the last load.
-        const bool two_terms = two_term_tile((wi.jlo + it) * kTile, row0);   // CTA-uniform
+        const bool two_terms = kMayTwo && two_term_tile((wi.jlo + it) * kTile, row0);   // CTA-uniform
+        uint32_t sr[kDqCols], dr[kDqCols];
+        tmem_ld32x2_wait(tmem + lane_off + kColS + wg * 32, sr, tmem + lane_off + kColDP + wg * 32, dr);
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sm.g_free));
+        if (it == 0 && fuse_d) {   // D of this item, computed by the D warps of this CTA an item ahead
+          if (!mbar_wait(w, smem_u32(&sm.d_ready[n & 1]), (n >> 1) & 1)) { ok = false; break; }
+          d_row = sm.d_row[n & 1][r];
+          dd2 = f2_pack(d_row, d_row);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sm.d_taken[n & 1]));
+        }
         // visible keys of this query within the 32 columns: lo <= col <= hi
         const bool edge_hi = ybase + kDqCols - 1 > row0;
         const bool edge_lo = window > 0 && ybase < row0 + kTile - 1 - window;
         const int hi = row - ybase;
         const int lo = window > 0 ? row - window - ybase : -(1 << 30);
-        uint32_t sr[kDqCols], dr[kDqCols];
         // Masking is a separate, rarely taken pass over the registers so that the main loop stays
         // branch-free.  The rows of a warp are consecutive, so a chunk that lane 0 sees up to its
         // last column (lane 31 from its first) is visible to the whole warp and is skipped.
-        auto load_masked = [&]() {
-          tmem_ld32x2_wait(tmem + lane_off + kColS + wg * 32, sr, tmem + lane_off + kColDP + wg * 32, dr);
-          if (edge_hi && 31 > hi - lane) {
+        if (edge_hi && 31 > hi - lane) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i > hi) sr[i] = 0xff800000u;   // -inf: P = 0
-          }
-          if (edge_lo && 0 < lo - lane + 31) {
+          for (int i = 0; i < 32; ++i)
+            if (i > hi) sr[i] = 0xff800000u;   // -inf: P = 0
+        }
+        if (edge_lo && 0 < lo - lane + 31) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < lo) sr[i] = 0xff800000u;
-          }
-        };
-        // dS' = P' (dP - D) for column pair i, with P' = kTruncGain * 2^(s*scale*log2e - lse*log2e)
-        // (the gain is divided out at the write-out); two-lane fp32 arithmetic, and three pairs in
-        // eight take the polynomial exp2 to relieve the special-function unit.
-        auto ds_pair = [&](int i, float& s0, float& s1) {
+          for (int i = 0; i < 32; ++i)
+            if (i < lo) sr[i] = 0xff800000u;
+        }
+        // dS' = P' (dP - D) with P' = kTruncGain * 2^(s*scale*log2e - lse*log2e), rounded to bf16 (the
+        // gain is divided out at the write-out); two-lane fp32 arithmetic, and three pairs in eight
+        // take the polynomial exp2 to relieve the special-function unit.
+        uint32_t pd[kDqCols / 2], pl[kDqCols / 2];
+#pragma unroll
+        for (int i = 0; i < kDqCols / 2; ++i) {
           const f32x2 x = f2_fma(f2_pack_u(sr[2 * i], sr[2 * i + 1]), sc2, nl2);
           float p0, p1;
           if ((i & 7) == 1 || (i & 7) == 4 || (i & 7) == 6) {
@@ -447,51 +423,64 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             p0 = ex2_approx(x0);
             p1 = ex2_approx(x1);
           }
-          f2_unpack(f2_mul(f2_pack(p0, p1), f2_sub(f2_pack_u(dr[2 * i], dr[2 * i + 1]), dd2)), s0, s1);
-        };
-        load_masked();
-        if (!two_terms) {
-          tc_fence_before();
-          mbar_arrive(smem_u32(&sm.g_free));
-        }
-        TRACE(0, g, 1);
-        if (it == 0 && fuse_d) {   // D of this item, computed by the D warps of this CTA an item ahead
-          if (!mbar_wait(w, smem_u32(&sm.d_ready[n & 1]), (n >> 1) & 1)) { ok = false; break; }
-          d_row = sm.d_row[n & 1][r];
-          dd2 = f2_pack(d_row, d_row);
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sm.d_taken[n & 1]));
-        }
-        uint32_t pd[kDqCols / 2], pl[kDqCols / 2];
-#pragma unroll
-        for (int i = 0; i < kDqCols / 2; ++i) {
           float s0, s1;
-          ds_pair(i, s0, s1);
-          pd[i] = pack_bf16x2_alu(s0, s1);   // rounded to bf16
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_sub(f2_pack_u(dr[2 * i], dr[2 * i + 1]), dd2)), s0, s1);
+          pd[i] = pack_bf16x2_alu(s0, s1);
+          if (kMayTwo)   // the rounding residual dS - bf16(dS), exact in fp32
+            pl[i] = pack_bf16x2_alu(s0 - bf16_lo_to_f32(pd[i]), s1 - bf16_hi_to_f32(pd[i]));
         }
-        if (two_terms) {
-          load_masked();
-          tc_fence_before();
-          mbar_arrive(smem_u32(&sm.g_free));
-#pragma unroll
-          for (int i = 0; i < kDqCols / 2; ++i) {
-            float s0, s1;
-            ds_pair(i, s0, s1);              // the same arithmetic: bit-identical to the first pass
-            pl[i] = pack_bf16x2_alu(s0 - bf16_lo_to_f32(pd[i]), s1 - bf16_hi_to_f32(pd[i]));   // exact in fp32
-          }
-        }
-        TRACE(0, g, 2);
         // the dQ MMAs of the previous tile must have consumed the dS region
         if (g > 0 && !mbar_wait(w, smem_u32(&sm.ds_free), (g - 1) & 1)) { ok = false; break; }
         tmem_st16(tmem + lane_off + kColDS + wg * 16, pd);
-        if (two_terms) tmem_st16(tmem + lane_off + kColDSLo + wg * 16, pl);
+        if (kMayTwo && two_terms) tmem_st16(tmem + lane_off + kColDSLo + wg * 16, pl);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.ready));
-        TRACE(0, g, 3);
       }
+      };
+      if (row0 == 0 || (window > 0 && window < 15)) tile_loop(std::true_type{});
+      else tile_loop(std::false_type{});
       if (!ok) break;
-      TRACE(0, 56 + (n & 3), 1);
+      if (wg < 2) {
+        if (!mbar_wait(w, smem_u32(&sm.acc_done), n & 1)) { ok = false; break; }
+        tc_fence_after();
+        // warpgroup c holds the (d, d+64) column-chunk pair c of its rows
+        uint32_t a[32], bq[32];
+        tmem_ld32x2_wait(tmem + lane_off + kColDQ + wg * 32, a, tmem + lane_off + kColDQ + 64 + wg * 32, bq);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.acc_free));
+        float lo_v[32], hi_v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          lo_v[i] = __uint_as_float(a[i]) * (p.scale * kTruncGainInv);   // dS carried the gain of P'
+          hi_v[i] = __uint_as_float(bq[i]) * (p.scale * kTruncGainInv);
+        }
+        if (p.cos_buf != nullptr) {
+          const int pos = min(row, T - 1);
+          const float4* cp = reinterpret_cast<const float4*>(p.cos_buf + (size_t)pos * 64 + wg * 32);
+          const float4* sp = reinterpret_cast<const float4*>(p.sin_buf + (size_t)pos * 64 + wg * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
+            rope_bwd_pair(lo_v[4 * i], hi_v[4 * i], cv.x, sv.x);
+            rope_bwd_pair(lo_v[4 * i + 1], hi_v[4 * i + 1], cv.y, sv.y);
+            rope_bwd_pair(lo_v[4 * i + 2], hi_v[4 * i + 2], cv.z, sv.z);
+            rope_bwd_pair(lo_v[4 * i + 3], hi_v[4 * i + 3], cv.w, sv.w);
+          }
+        }
+        // transposition buffer of this warp: 2 KB of the V slot that held the item's last V tile
+        const uint32_t epi = smem_u32(sm.v[(g - 1) % kDqVStages]) + warp * 2048u;
+        const int esize = p.grad_f32 ? 4 : 2;
+        const size_t row_stride = (size_t)H * 128 * esize;
+        const int wrow0 = row0 + 32 * (warp & 3);
+        uint8_t* gout = static_cast<uint8_t*>(p.dq) + (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
+        warp_store_32cols(epi, lane, lo_v, gout + (size_t)(wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
+        warp_store_32cols(epi, lane, hi_v, gout + (size_t)(64 + wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
+        fence_proxy_async_smem();   // the slot is next written by a bulk tensor load
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.epi_free));
+      }
       ++n;
     }
   }
@@ -501,7 +490,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (warp == kDqCW + 1) tmem_dealloc(tmem, 512);
 }
 
-AR_TRACE_READER(ar_debug_dq_trace)
 
 // The operand maps are built with 64-row boxes.
 cudaError_t launch_attn_bwd_dq(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,

@@ -344,19 +344,4 @@ __device__ __forceinline__ void drain_if_aborted(uint32_t abort_smem) {
   }
 }
 
-
-// Optional event trace (compiled in with -DAR_TRACE, never in the shipped build): one chosen CTA
-// records clock64() at named points of each role's loop; `trace_on` is a bool the kernel defines.
-#ifdef AR_TRACE
-static __device__ unsigned long long g_trace[4 * 64 * 8];
-#define TRACE(role, it, ev) do { if (trace_on && (it) < 64) g_trace[((role) * 64 + (it)) * 8 + (ev)] = clock64(); } while (0)
-#define AR_TRACE_READER(name)                                                             \
-  extern "C" __attribute__((visibility("default"))) void name(unsigned long long* out) {  \
-    cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));                                  \
-  }
-#else
-#define TRACE(role, it, ev)
-#define AR_TRACE_READER(name)
-#endif
-
 }  // namespace ar

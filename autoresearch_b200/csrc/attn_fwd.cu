@@ -96,9 +96,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   grid_dep_launch_dependents();   // all CTAs of this grid are resident: the next kernel may be scheduled
   WaitCtx w{p.status, smem_u32(&sm.abort_flag)};
-#ifdef AR_TRACE
-  const bool trace_on = blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 4 || warp == 13 || warp == 14);
-#endif
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&sm.q_full), 1);
@@ -123,7 +120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     sm.exp_cnt[0] = 0;
     sm.exp_cnt[1] = 0;
-    sm.abort_flag = (*p.status != 0u) ? 1u : 0u;   // an earlier abandoned wait: do no work
+    sm.abort_flag = 0u;
     fence_mbar_init();
     prefetch_tmap(&map_q);
     prefetch_tmap(&map_k);
@@ -137,6 +134,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   grid_dep_wait();   // everything above overlapped the previous kernel's tail; its results are visible from here
+  // An earlier abandoned wait (this or a previous kernel's, status word still set): do no work.  The
+  // word is read only now, when the previous kernel's writes are visible.  Without data from the TMA
+  // warp no hand-shake of this CTA can complete, so it is enough that the producers stay idle: every
+  // other role gives up at its first wait.
+  if (threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) sm.abort_flag = 1u;
+  __syncthreads();
+  const bool live = ld_shared_u32(smem_u32(&sm.abort_flag)) == 0u;
   const uint32_t tmem = sm.tmem_base;
 
   if (warp < 8) {
@@ -183,7 +187,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         fence_proxy_async_smem();
         mbar_arrive(smem_u32(&sm.q_ready[X]));
       }
-      TRACE(X, 56 + (n & 3), 0);
 
       // m_ref: the reference maximum P is computed against (raw score units).  It trails the
       // true running maximum by at most kLazyRescaleLog2 (in log2 units after scaling).
@@ -194,10 +197,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         // step is complete as well once this wait returns.
         if (!mbar_wait(w, s_full, (g_own + it) & 1)) { ok = false; break; }
         tc_fence_after();
-        TRACE(X, g_own + it, 0);
         uint32_t sr[128];
         tmem_ld128_wait(tS, sr);
-        TRACE(X, g_own + it, 1);
         const bool edge_hi = kbase + kTile - 1 > qlo;
         const bool edge_lo = window > 0 && kbase < qlo + kTile - 1 - window;
         if (edge_hi || edge_lo) {
@@ -237,7 +238,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           alpha = ex2_approx((m_ref - mx) * p.scale_log2e);   // m_ref = -inf gives 0
           m_ref = mx;
         }
-        TRACE(X, g_own + it, 2);
         // Rare: the running maximum outgrew the lazy threshold, rescale O before any P V of this
         // step is issued (the P V of the previous step is complete: s_full's commit covered it).
         if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -266,7 +266,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         } else {
           if (it < n_other && !counter_wait(w, smem_u32(&sm.exp_cnt[0]), 4u * (uint32_t)(g_oth + it + 1))) { ok = false; break; }
         }
-        TRACE(X, g_own + it, 3);
         // P = 2^(s*scale*log2e - m*scale*log2e) * kTruncGain, truncated to bf16 (see ptx.cuh).
         // Three pairs in eight take the polynomial path (FMA pipe), five the special-function
         // unit, which at 16 results per clock per SM would otherwise need as long for a tile as
@@ -293,7 +292,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             else sum_a = f2_add(sum_a, f2_pack(p0, p1));
             pk[i] = pack_bf16x2_trunc(p0, p1);
           }
-          TRACE(X, g_own + it, 4 + 2 * c);
           tmem_st32(tS + c * 32, pk);
           if (c == 1) {
             __syncwarp();
@@ -302,14 +300,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tmem_wait_st();
           tc_fence_before();
           mbar_arrive(p_ready + 8 * c);
-          TRACE(X, g_own + it, 5 + 2 * c);
         }
         float sum0, sum1;
         f2_unpack(f2_add(sum_a, sum_b), sum0, sum1);
         l_run = l_run * alpha + (sum0 + sum1);
       }
       if (!ok) break;
-      TRACE(X, 56 + (n & 3), 1);
 
       if (!kRope) {
         // Hand the row statistics to the write-out warps.  They live in the transposition buffers
@@ -331,7 +327,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // epilogue: O / l and LSE = m * scale + ln(l)   (ops.mojo:316-321)
       if (!mbar_wait(w, smem_u32(&sm.o_final[X]), nx & 1)) { ok = false; break; }
       tc_fence_after();
-      TRACE(X, 56 + (n & 3), 2);
       uint32_t og[128];
       tmem_ld128_wait(tO, og);
       tc_fence_before();
@@ -379,7 +374,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       if (qrow < T) p.lse[((size_t)wi.b * T + qrow) * p.dims.H + wi.h] = m_ref * p.scale + logf(l_run);
-      TRACE(X, 56 + (n & 3), 3);
       g_own += n_it;
       g_oth += n_other;
       ++nx;
@@ -391,7 +385,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     if (warp == kWarpTma) {
       // ------------------------------------------------------------------ TMA producer
       int g = 0, n = 0;   // KV tiles and items issued so far
-      bool ok = true;
+      bool ok = live;
       for (int kk = 0; ok; ++kk) {
         const int item = sched_item(kk, n_items);
         if (item == -1) break;
@@ -514,7 +508,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const int itx = j - jlo_x;
           if (itx == 0 && !issue_qk(j)) { ok = false; break; }
           if (!mbar_wait(w, smem_u32(&sm.p_ready[X][0]), (gx + itx) & 1)) { ok = false; break; }
-          TRACE(2 + X, gx + itx, 0);
           if (!mbar_wait(w, smem_u32(&sm.v_full[s]), parity_of(j))) { ok = false; break; }
           // the item's first P V overwrites O_X: the previous item's rows must have left
           if (itx == 0 && nx > 0 && !mbar_wait(w, smem_u32(&sm.o_free[X]), (nx - 1) & 1)) { ok = false; break; }
@@ -526,20 +519,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int ks = 0; ks < 4; ++ks)
             umma_ts_elect(tO, tS + ks * 8, make_sdesc_sw128(va + ks * 2048, kHalfBytes, 1024), idesc_pv,
                           (itx > 0 || ks > 0) ? 1u : 0u);
-          TRACE(2 + X, gx + itx, 1);
           if (!mbar_wait(w, smem_u32(&sm.p_ready[X][1]), (gx + itx) & 1)) { ok = false; break; }
           tc_fence_after();
-          TRACE(2 + X, gx + itx, 2);
 #pragma unroll
           for (int ks = 4; ks < 8; ++ks)
             umma_ts_elect(tO, tS + ks * 8, make_sdesc_sw128(va + ks * 2048, kHalfBytes, 1024), idesc_pv, 1u);
-          TRACE(2 + X, gx + itx, 3);
           if (j == jhi_x) umma_commit_elect(smem_u32(&sm.o_final[X]));
           umma_commit_elect(smem_u32(&sm.v_empty[s]));
           // S_X of the next KV tile overwrites the columns P_X occupies: it is issued by the
           // same thread after the P V MMAs, and MMAs of one thread complete in issue order.
           if (active(j + 1) && j + 1 <= wi.jhi && !issue_qk(j + 1)) { ok = false; break; }
-          TRACE(2 + X, gx + itx, 4);
         }
         if (!ok) break;
         g0 += n_kv;
@@ -655,7 +644,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == kWarpMma) tmem_dealloc(tmem, 512);
 }
 
-AR_TRACE_READER(ar_debug_fwd_trace)
 
 size_t attn_fwd_smem_bytes() { return sizeof(FwdSmem) + 1024; }
 

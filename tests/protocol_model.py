@@ -199,7 +199,7 @@ def run_dkv(B,H,T,W,c,G=148):
     n_items=((T+127)//128)*B*H
     bars={}
     def mk(n,cnt): bars[n]=Bar(n,cnt)
-    mk('x_full',1); mk('x_free',2); mk('acc_done',2); mk('acc_free0',1); mk('acc_free1',1)
+    mk('x_full',1); mk('x_free',2); mk('acc_done',2); mk('acc_free',2)
     for s in range(4): mk(f'y_full{s}',1); mk(f'y_empty{s}',2)
     for i in range(2): mk(f'g_full{i}',2); mk(f'ready{i}',2)
     def tma():
@@ -218,7 +218,7 @@ def run_dkv(B,H,T,W,c,G=148):
             def acc(it,gg):
                 s=gg%4; bf=gg&1
                 yield ('wait',f'ready{bf}',(gg>>1)&1)
-                if it==0 and n>0: yield ('wait',f'acc_free{I}',(n-1)&1)
+                if it==0 and n>0: yield ('wait','acc_free',(n-1)&1)
                 yield ('arrive',f'y_empty{s}',1)
             yield ('wait','x_full',n&1)
             for it in range(ns):
@@ -240,15 +240,10 @@ def run_dkv(B,H,T,W,c,G=148):
                 yield ('wait',f'g_full{bf}',(gg>>1)&1)
                 yield ('arrive',f'ready{bf}',1)
             g0+=ns
-            n+=1
-    def store():
-        n=0
-        for item in items_of(c,G,n_items):
             yield ('wait','acc_done',n&1)
-            yield ('arrive','acc_free0',1)    # dV read
-            yield ('arrive','acc_free1',1)    # dK read
+            yield ('arrive','acc_free',1)
             n+=1
-    return drive({'tma':tma(),'is0':issuer(0),'is1':issuer(1),'wg0':compute(0),'wg1':compute(1),'st':store()},bars,f"dkv cta {c}")
+    return drive({'tma':tma(),'is0':issuer(0),'is1':issuer(1),'wg0':compute(0),'wg1':compute(1)},bars,f"dkv cta {c}")
 def dq_item(item,B,H,T,W,n_qt):
     bh=B*H; qi=item//bh; row0=(n_qt-1-qi)*128
     klo=max(0,row0-W) if W>0 else 0; khi=min(row0+127,T-1)
@@ -258,7 +253,7 @@ def run_dq(B,H,T,W,c,fuse,G=148):
     bars={}
     def mk(n,cnt): bars[n]=Bar(n,cnt)
     mk('x_full',1); mk('x_free',2); mk('g_full',2); mk('g_free',4); mk('ready',4); mk('ds_free',1)
-    mk('acc_done',1); mk('acc_free',1); mk('epi_free',1)
+    mk('acc_done',1); mk('acc_free',2); mk('epi_free',2)
     for s in range(3): mk(f'k_full{s}',1); mk(f'k_empty{s}',2)
     for s in range(2): mk(f'v_full{s}',1); mk(f'v_empty{s}',1); mk(f'd_ready{s}',1); mk(f'd_taken{s}',4)
     def tma():
@@ -302,17 +297,10 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 g+=1
             yield ('arrive','acc_done',1); n+=1
     def dwarps():
-        # D of item n (when fused), then the write-out of item n-1
         n=0
         for item in items_of(c,G,n_items):
-            if fuse:
-                if n>1: yield ('wait',f'd_taken{n&1}',((n>>1)-1)&1)
-                yield ('arrive',f'd_ready{n&1}',1)
-            if n>0:
-                yield ('wait','acc_done',(n-1)&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
-            n+=1
-        if n>0:
-            yield ('wait','acc_done',(n-1)&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
+            if n>1: yield ('wait',f'd_taken{n&1}',((n>>1)-1)&1)
+            yield ('arrive',f'd_ready{n&1}',1); n+=1
     def compute(wg):
         g=0;n=0
         for item in items_of(c,G,n_items):
@@ -325,7 +313,10 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 if g>0: yield ('wait','ds_free',(g-1)&1)
                 yield ('arrive','ready',1)
                 g+=1
+            if wg<2:
+                yield ('wait','acc_done',n&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
             n+=1
-    ag={'tma':tma(),'isS':issuer(0),'isP':issuer(1),'isQ':dqiss(),'dw':dwarps()}
+    ag={'tma':tma(),'isS':issuer(0),'isP':issuer(1),'isQ':dqiss()}
     for wg in range(4): ag[f'wg{wg}']=compute(wg)
+    if fuse: ag['dw']=dwarps()
     return drive(ag,bars,f"dq cta {c} fuse {fuse}")

@@ -37,11 +37,13 @@ def test_prologue_matches_rope_then_rmsnorm(cuda_device, B, T, H):
     q_rot, k_rot, v_b, rms_q, rms_k = _prologue(q, k, v, cos, sin, T)
     torch.cuda.synchronize()
     qo, ko, rq, rk = orc.qk_rope_norm(qh, kh, cos_h, sin_h, T)
-    # bf16 outputs: half an ulp, 2^-9 of the magnitude (normalised rows: |y| < 8) on top of fp32 rounding
+    # bf16 outputs: each element within half a bf16 ulp (at most 2^-8 of its magnitude) of the oracle's
+    # fp32 value, and - up to the rare element where the two summation orders of the mean square
+    # land on different sides of a rounding boundary - equal to the oracle's value rounded to bf16
     for name, got, want in (("q_rot", q_rot, qo), ("k_rot", k_rot, ko), ("v", v_b, vh)):
         g = got.float().cpu().numpy()
-        assert np.abs(g - want).max() <= np.abs(want).max() / 512 + 1e-6, name
-        assert np.array_equal(g, orc.to_bf16_rne(want)) or np.mean(g != orc.to_bf16_rne(want)) < 1e-3, name
+        assert (np.abs(g - want) <= np.abs(want) / 256 + 1e-6).all(), name
+        assert np.mean(g != orc.to_bf16_rne(want)) < 1e-3, name
     assert np.allclose(rms_q.cpu().numpy(), rq, rtol=2e-6) and np.allclose(rms_k.cpu().numpy(), rk, rtol=2e-6)
 
 

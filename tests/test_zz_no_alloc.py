@@ -29,6 +29,7 @@ def _call(fn, o, lse, q, k, v, B, T, H, W):
 def test_noalloc_forward_matches_allocating_entry_point_twice(cuda_device):
     import torch
     L = ab.lib()
+    L.ar_noalloc_status()      # start clean: reads and clears whatever an earlier test left behind
     for call, (B, T, H, W, seed) in enumerate([(2, 384, 4, 100, 21), (1, 1000, 3, 0, 22)]):
         assert B * T * H <= 16384
         g = torch.Generator(device="cuda").manual_seed(seed)
