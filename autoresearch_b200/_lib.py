@@ -57,7 +57,7 @@ SIGNATURES = {
     "ar_selftest_wait_timeout": (ctypes.c_int32, [ctypes.c_int32, _vp]),
     "ar_rope_fwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "ar_rope_bwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
-    "ar_qk_norm_rope_cast": (ctypes.c_int32, [_vp] * 10 + [_i64] * 4 + [ctypes.c_float, _vp]),
+    "ar_qk_norm_rope_cast": (ctypes.c_int32, [_vp] * 8 + [ctypes.c_int32, _vp, _vp] + [_i64] * 4 + [ctypes.c_float, _vp]),
     "ar_flash_attn_fwd": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "ar_flash_attn_fwd_noalloc": (ctypes.c_int32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "ar_noalloc_status": (ctypes.c_int32, []),

@@ -264,9 +264,11 @@ AR_API ar_status ar_rope_bwd(float* grad_in, const float* grad_out, const float*
 }
 
 AR_API ar_status ar_qk_norm_rope_cast(void* q_rot, void* k_rot, void* v_bf16, float* rms_q, float* rms_k,
-                                      const float* q, const float* k, const float* v, const float* cos_buf,
-                                      const float* sin_buf, int64_t num_tokens, int64_t num_heads,
-                                      int64_t head_dim, int64_t seq_len, float eps, void* stream) {
+                                      const void* q, const void* k, const void* v, int32_t in_dtype,
+                                      const float* cos_buf, const float* sin_buf, int64_t num_tokens,
+                                      int64_t num_heads, int64_t head_dim, int64_t seq_len, float eps,
+                                      void* stream) {
+  if (in_dtype != AR_F32 && in_dtype != AR_BF16) return fail(AR_ERR_UNSUPPORTED, "in_dtype %d unknown", in_dtype);
   if (!q_rot || !k_rot || !q || !k || !cos_buf || !sin_buf) return fail(AR_ERR_BAD_ARG, "null pointer");
   if ((v == nullptr) != (v_bf16 == nullptr)) return fail(AR_ERR_BAD_ARG, "v and v_bf16 must be given together");
   if (num_tokens <= 0 || num_heads <= 0) return fail(AR_ERR_BAD_ARG, "num_tokens, num_heads must be positive");
@@ -277,10 +279,19 @@ AR_API ar_status ar_qk_norm_rope_cast(void* q_rot, void* k_rot, void* v_bf16, fl
     return fail(AR_ERR_BAD_ARG, "tensor pointers must be 16-byte aligned");
   DeviceState* st;
   AR_TRY(device_state(&st));
-  AR_CUDA(launch_qk_norm_rope_cast_128(static_cast<__nv_bfloat16*>(q_rot), static_cast<__nv_bfloat16*>(k_rot),
-                                       static_cast<__nv_bfloat16*>(v_bf16), rms_q, rms_k, q, k, v, cos_buf, sin_buf,
-                                       num_tokens * num_heads, (int)num_heads, seq_len, eps, (cudaStream_t)stream),
-          "qk_norm_rope_cast launch");
+  auto* qo = static_cast<__nv_bfloat16*>(q_rot);
+  auto* ko = static_cast<__nv_bfloat16*>(k_rot);
+  auto* vo = static_cast<__nv_bfloat16*>(v_bf16);
+  const long long rows = num_tokens * num_heads;
+  if (in_dtype == AR_F32)
+    AR_CUDA(launch_qk_norm_rope_cast_128<float>(qo, ko, vo, rms_q, rms_k, (const float*)q, (const float*)k, (const float*)v,
+                                                cos_buf, sin_buf, rows, (int)num_heads, seq_len, eps, (cudaStream_t)stream),
+            "qk_norm_rope_cast launch");
+  else
+    AR_CUDA(launch_qk_norm_rope_cast_128<__nv_bfloat16>(qo, ko, vo, rms_q, rms_k, (const __nv_bfloat16*)q,
+                                                        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, cos_buf, sin_buf,
+                                                        rows, (int)num_heads, seq_len, eps, (cudaStream_t)stream),
+            "qk_norm_rope_cast launch");
   return AR_OK;
 }
 

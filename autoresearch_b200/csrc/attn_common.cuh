@@ -74,8 +74,9 @@ cudaError_t launch_rope_pair_bf16_128(__nv_bfloat16* out0, const __nv_bfloat16* 
                                       long long tokens, int num_heads, long long seq_len, cudaStream_t stream);
 // rope_fwd + per-head rmsnorm_fwd on q, k and the bf16 cast of q, k, v in one launch (head_dim 128);
 // v / v_out may be null (q and k only); rms_q / rms_k may be null.
+template <typename InT>
 cudaError_t launch_qk_norm_rope_cast_128(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* rms_q,
-                                         float* rms_k, const float* q, const float* k, const float* v,
+                                         float* rms_k, const InT* q, const InT* k, const InT* v,
                                          const float* cos_buf, const float* sin_buf, long long rows, int num_heads,
                                          long long seq_len, float eps, cudaStream_t stream);
 cudaError_t launch_rope_scalar(float* out, const float* in, const float* cos_buf,

@@ -117,14 +117,15 @@ rope_pair_bf16_128_kernel(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bf
 // reference the row is rotated first and normalised by sqrt(mean(y^2) + eps) of the ROTATED row
 // (a rotation keeps the sum of squares, so this differs from normalising first only by rounding).
 // rms_q / rms_k (optional) receive that square root per row, as rmsnorm_fwd's rms_out does.
+template <typename InT>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_cast_128_kernel(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* rms_q,
-                             float* rms_k, const float* __restrict__ q, const float* __restrict__ k,
-                             const float* __restrict__ v, const float* __restrict__ cos_buf,
+                             float* rms_k, const InT* __restrict__ q, const InT* __restrict__ k,
+                             const InT* __restrict__ v, const float* __restrict__ cos_buf,
                              const float* __restrict__ sin_buf, long long rows, int num_heads, long long seq_len,
                              float eps) {
   const int which = blockIdx.y;   // 0: q, 1: k, 2: v
-  const float* in = which == 0 ? q : (which == 1 ? k : v);
+  const InT* in = which == 0 ? q : (which == 1 ? k : v);
   __nv_bfloat16* out = which == 0 ? q_out : (which == 1 ? k_out : v_out);
   float* rms_out = which == 0 ? rms_q : (which == 1 ? rms_k : nullptr);
   const long long total = rows * 8;   // a multiple of 8: the 8 threads of a row always run together
@@ -133,8 +134,8 @@ qk_norm_rope_cast_128_kernel(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bf
     const long long row = tid >> 3;
     const int g = static_cast<int>(tid & 7);
     const long long base = row * 128 + g * 8;
-    const float4 a0 = *reinterpret_cast<const float4*>(in + base), a1 = *reinterpret_cast<const float4*>(in + base + 4);
-    const float4 b0 = *reinterpret_cast<const float4*>(in + base + 64), b1 = *reinterpret_cast<const float4*>(in + base + 68);
+    const float4 a0 = Vec4<InT>::load(in + base), a1 = Vec4<InT>::load(in + base + 4);
+    const float4 b0 = Vec4<InT>::load(in + base + 64), b1 = Vec4<InT>::load(in + base + 68);
     float x1[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
     float x2[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
     if (which < 2) {
@@ -174,17 +175,25 @@ qk_norm_rope_cast_128_kernel(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bf
   }
 }
 
+template <typename InT>
 cudaError_t launch_qk_norm_rope_cast_128(__nv_bfloat16* q_out, __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* rms_q,
-                                         float* rms_k, const float* q, const float* k, const float* v,
+                                         float* rms_k, const InT* q, const InT* k, const InT* v,
                                          const float* cos_buf, const float* sin_buf, long long rows, int num_heads,
                                          long long seq_len, float eps, cudaStream_t stream) {
   long long blocks = (rows * 8 + 255) / 256;
   const long long cap = 148LL * 16;   // grid-stride beyond 16 blocks (of 256 threads) per SM
   dim3 grid(static_cast<unsigned>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks)), v != nullptr ? 3 : 2);
-  qk_norm_rope_cast_128_kernel<<<grid, 256, 0, stream>>>(q_out, k_out, v_out, rms_q, rms_k, q, k, v, cos_buf, sin_buf,
-                                                         rows, num_heads, seq_len, eps);
+  qk_norm_rope_cast_128_kernel<InT><<<grid, 256, 0, stream>>>(q_out, k_out, v_out, rms_q, rms_k, q, k, v, cos_buf, sin_buf,
+                                                              rows, num_heads, seq_len, eps);
   return cudaGetLastError();
 }
+template cudaError_t launch_qk_norm_rope_cast_128<float>(__nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, float*, float*,
+                                                         const float*, const float*, const float*, const float*,
+                                                         const float*, long long, int, long long, float, cudaStream_t);
+template cudaError_t launch_qk_norm_rope_cast_128<__nv_bfloat16>(__nv_bfloat16*, __nv_bfloat16*, __nv_bfloat16*, float*, float*,
+                                                                 const __nv_bfloat16*, const __nv_bfloat16*,
+                                                                 const __nv_bfloat16*, const float*, const float*,
+                                                                 long long, int, long long, float, cudaStream_t);
 
 // Scalar form for head dims whose half is not a multiple of 4 (fp32 only; the rope mirrors).
 __global__ void __launch_bounds__(256)

@@ -49,9 +49,11 @@ C5 = dict(B=128, H=8, T=2048, windows=(1024, 1024, 1024, 2048))       # BASELINE
 # DRAM bytes per launch (dram__bytes_read.sum, dram__bytes_write.sum) from an ncu capture of
 # full-size launches: B=16, H=4, T=2048, W=1024, 64 (b,h) units; other unit counts scale it.
 NCU_DRAM = {
-    "attn_fwd": (125.0e6, 13.0e6), "attn_bwd_dq": (253.7e6, 40.0e6), "attn_bwd_dkv": (159.9e6, 82.3e6),
+    "attn_fwd": (126.8e6, 9.9e6), "attn_bwd_dq": (265.3e6, 38.2e6), "attn_bwd_dkv": (157.0e6, 79.2e6),
     "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:attn_ "
-              "on one forward+backward of B=16 H=4 T=2048 W=1024 (per launch; scaled by the unit count)",
+              "-s 36 -c 12 on `bench.py --steps 2 --warmup 3 --no-e2e --no-cpu --no-sustained --no-config5 "
+              "--no-phases` (B=16 H=4 T=2048; mean of the three W=1024 launches of each kernel; "
+              "scaled by the unit count)",
 }
 
 
@@ -369,13 +371,42 @@ def run_gpu(args):
             kernels[name] = {"flop_per_pair": pp * D, "ms_per_step": round(phase[name], 4), "launches_per_step": nl,
                              "achieved": ach, "frac": ach / peak,
                              "traffic": (rd + wr) * (B * H) / 64.0 if T == 2048 else None}
-        rope_ms = phase["fwd_total(rope+attn_fwd)"] - phase["attn_fwd"]
-        if args.rope == "saved" and rope_ms > 0:
-            # forward rotation of Q and K (one launch per layer): 2 tensors read + 2 written, bf16
-            nbytes = 4 * B * T * H * D * 2 * nl
-            kernels["rope_pair_bf16_128"] = {"bound": "hbm", "ms_per_step": round(rope_ms, 4), "launches_per_step": nl,
-                                             "achieved": nbytes / (rope_ms * 1e-3) / 1e9, "unit": "GB/s",
-                                             "frac": nbytes / (rope_ms * 1e-3) / 1e9 / hbm_gbs, "peak": hbm_gbs}
+        # forward rotation of Q and K (one launch per layer): the backward entry point with all three of
+        # its stages skipped and no saved rotated tensors launches exactly that kernel, into scratch
+        rope_only = []
+        for L in layers:
+            p = ab.AttnParams(window=L["w"], rope=tables, skip_d=True, skip_dq=True, skip_dkv=True)
+            rope_only.append(p)
+        rope_ms = timed(lambda: [bwd(L, p) for L, p in zip(layers, rope_only)], reps) / reps
+        nbytes = 4 * B * T * H * D * 2 * nl       # 2 tensors read + 2 written, bf16
+        kernels["rope_pair_bf16_128"] = {"bound": "hbm", "ms_per_step": round(rope_ms, 4), "launches_per_step": nl,
+                                         "achieved": nbytes / (rope_ms * 1e-3) / 1e9, "unit": "GB/s",
+                                         "frac": nbytes / (rope_ms * 1e-3) / 1e9 / hbm_gbs, "peak": hbm_gbs, "bytes": nbytes // nl}
+        # the HBM-bound kernels around the path, each through its C-ABI entry point at this size:
+        # algorithmic bytes (tensors read + written once) over the device time of one launch
+        n_el = B * T * H * D
+        f32 = [torch.randn(B, T, H, D, device=dev, generator=gen) for _ in range(3)]
+        b16 = [torch.empty(B, T, H, D, device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        dsc = torch.empty(B, T, H, device=dev)
+        L_ = _lib.lib()
+        st_ = torch.cuda.current_stream().cuda_stream
+
+        def hbm_kernel(name, fn, nbytes, what):
+            fn()
+            ms = timed(fn, 10) / 10
+            kernels[name] = {"bound": "hbm", "ms_per_launch": round(ms, 4), "achieved": nbytes / (ms * 1e-3) / 1e9,
+                             "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / hbm_gbs, "peak": hbm_gbs, "bytes": nbytes,
+                             "what": what}
+
+        hbm_kernel("qk_norm_rope_cast_128", lambda: _lib.check(L_.ar_qk_norm_rope_cast(
+            b16[0].data_ptr(), b16[1].data_ptr(), b16[2].data_ptr(), None, None, f32[0].data_ptr(), f32[1].data_ptr(),
+            f32[2].data_ptr(), _lib.AR_F32, tables[0].data_ptr(), tables[1].data_ptr(), B * T, H, D, T, 1e-5, st_)),
+            n_el * (3 * 4 + 3 * 2), "ar_qk_norm_rope_cast: fp32 q, k, v in, bf16 rotated+normalised q, k and bf16 v out")
+        hbm_kernel("rope_cast<f32,f32>", lambda: ab.rope_fwd(f32[0], f32[0], tables[0], tables[1], B * T, H, D, T),
+                   n_el * 8, "ar_rope_fwd in place on one fp32 tensor")
+        hbm_kernel("precompute_d128<f32>", lambda: ab.flash_attn_bwd_precompute_d(dsc, f32[1], f32[2], B, T, H, D),
+                   n_el * 8 + B * T * H * 4, "ar_flash_attn_bwd_precompute_d on fp32 O, dO")
+        del f32, b16, dsc
         dominant = max(per_pair, key=lambda n: phase[n])
         kd = kernels[dominant]
         roofline = {"bound": "tensor", "kernel": dominant, "achieved": kd["achieved"], "peak": peak, "unit": "TFLOP/s",
@@ -561,14 +592,88 @@ def run_gpu(args):
     print(json.dumps(line))
 
 
+def run_config3(args):
+    """BASELINE config 3: forward + backward of the reference's small GPT (depth 8, d_model 512, 4 heads of
+    128, vocabulary 8192, T=2048, B=16 per GPU; token ids uniform, seeded) with the attention path on
+    libarattn.so and the other layers as torch operations; under torchrun each rank takes its own batch
+    and the gradients are all-reduced in per-layer buckets over NCCL.  Reports tokens/s of the whole step
+    and the share of the step's device time spent in the attention calls."""
+    import torch
+
+    import autoresearch_b200 as ab
+    from autoresearch_b200 import train_step as ts
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    cfg = ab.GPTConfig()                       # depth 8, 512 wide, 4 heads of 128, vocabulary 8192, T = 2048
+    B, T = args.batch or 16, cfg.sequence_len
+    weights = ts.init_weights(cfg, dev, test_init=True)     # non-zero c_proj / mlp_proj (test_forward.mojo:48-63)
+    attn = ts.LibraryAttention(cfg, T, dev)
+    step = ts.TrainStep(cfg, weights, attn, reference_quirks=True, process_group=True if world > 1 else None)
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (B, T), device=dev, generator=gen)
+    targets = torch.cat([ids[:, 1:], torch.randint(0, cfg.vocab_size, (B, 1), device=dev, generator=gen)], dim=1)
+    steps = max(1, min(args.steps, 10))
+    loss = None
+    for _ in range(3):
+        step.zero_grads()
+        loss = step.step(ids, targets)
+    attn.attention_ms()                        # reset
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step.zero_grads()
+        loss = step.step(ids, targets)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    attn_ms = attn.attention_ms() / steps
+    ab.check_device_status()
+    if dist is not None:
+        t = torch.tensor([ms, attn_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, attn_ms = float(t[0]), float(t[1])
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    windows = [cfg.window_size(i) for i in range(cfg.n_layer)]
+    attn_flops = flops(14, T, windows, B, cfg.n_head)
+    n_param = sum(v.numel() for v in weights.values())
+    print(json.dumps({
+        "metric": "gpt_train_step_tokens_per_s", "value": world * B * T / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "BASELINE config 3 per GPU: small-GPT forward + backward, attention on libarattn.so, other "
+                               "layers torch (cuBLAS bf16 matmuls, fp32 residual stream)", "B_per_gpu": B, "T": T,
+                   "n_layer": cfg.n_layer, "n_embd": cfg.n_embd, "n_head": cfg.n_head, "vocab": cfg.vocab_size,
+                   "windows": windows, "parameters": n_param, "backward": "as the reference computes it",
+                   "parallelism": f"data parallel over {world} rank(s), per-layer gradient buckets all-reduced with NCCL"},
+        "loss": float(loss),
+        "attention": {"ms_per_step": attn_ms, "share_of_step": attn_ms / ms,
+                      "tflops": attn_flops / (attn_ms * 1e-3) / 1e12,
+                      "calls": "prologue (rope + qk-norm + cast) + forward + backward, 8 layers"},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS),
-                    help="BASELINE config: 2 = default-model SSSL group (the headline), 4 = long context T=8192")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4],
+                    help="BASELINE config: 2 = default-model SSSL group (the headline), 3 = full small-GPT train step, "
+                         "4 = long context T=8192")
     ap.add_argument("--batch", type=int, default=0,
                     help="batch per GPU instead of the config's (a small case for profilers); 0 = the config's")
     ap.add_argument("--rope", default="saved", choices=["saved", "fused", "prepass"],
@@ -582,7 +687,11 @@ def main():
     ap.add_argument("--no-config5", action="store_true", help="skip the config-5 strong-scaling object")
     args = ap.parse_args()
     if args.impl == "reference":
+        if args.config == 3:
+            args.config = 2      # the host-core arm times the attention path, which is what it restates
         run_reference(args)
+    elif args.config == 3:
+        run_config3(args)
     else:
         run_gpu(args)
 

@@ -103,7 +103,8 @@ AR_API ar_status ar_rope_bwd(float* grad_in, const float* grad_out, const float*
 /* The step before attention in one launch: replaces the two rope_fwd launches and the two per-head
  * rmsnorm_fwd launches on q and k (model.mojo:668-687; ops.mojo:209-217, 61-67) and writes the
  * bf16 operands the fused family reads, so that the trainer's fp32 q, k, v (outputs of its QKV
- * projections, model.mojo:643-645) reach the tensor-core kernels with one pass over memory:
+ * projections, model.mojo:643-645; in_dtype AR_F32, or AR_BF16 for a caller whose projections
+ * already produce bf16) reach the tensor-core kernels with one pass over memory:
  *     q_rot = bf16( rope(q) / sqrt(mean(rope(q)^2) + eps) )   per (token, head) row, same for k
  *     v_bf16 = bf16(v)                                       (v, v_bf16 may both be NULL)
  * q_rot, k_rot, v_bf16: bf16 [num_tokens, num_heads, 128].  rms_q, rms_k (optional, fp32
@@ -114,8 +115,8 @@ AR_API ar_status ar_rope_bwd(float* grad_in, const float* grad_out, const float*
  * what the reference computes, whose backward passes gradients straight through this
  * normalisation (model.mojo:937). */
 AR_API ar_status ar_qk_norm_rope_cast(void* q_rot, void* k_rot, void* v_bf16, float* rms_q,
-                                      float* rms_k, const float* q, const float* k, const float* v,
-                                      const float* cos_buf, const float* sin_buf,
+                                      float* rms_k, const void* q, const void* k, const void* v,
+                                      int32_t in_dtype, const float* cos_buf, const float* sin_buf,
                                       int64_t num_tokens, int64_t num_heads, int64_t head_dim,
                                       int64_t seq_len, float eps, void* stream);
 

@@ -21,7 +21,8 @@ def _prologue(q, k, v, cos, sin, T, want_rms=True):
     rms_k = torch.empty(B, T, H, device="cuda") if want_rms else None
     st = ab.lib().ar_qk_norm_rope_cast(
         q_rot.data_ptr(), k_rot.data_ptr(), v_b.data_ptr(), rms_q.data_ptr() if want_rms else None,
-        rms_k.data_ptr() if want_rms else None, q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(),
+        rms_k.data_ptr() if want_rms else None, q.data_ptr(), k.data_ptr(), v.data_ptr(),
+        _lib.AR_F32 if q.dtype == torch.float32 else _lib.AR_BF16, cos.data_ptr(),
         sin.data_ptr(), B * T, H, D, T, 1e-5, torch.cuda.current_stream().cuda_stream)
     assert st == _lib.AR_OK, ab.lib().ar_last_error()
     return q_rot, k_rot, v_b, rms_q, rms_k
