@@ -46,6 +46,7 @@ class ArAttnParams(ctypes.Structure):
         ("workspace", _vp), ("workspace_bytes", ctypes.c_uint64),
         ("stream", _vp),
         ("q_rot", _vp), ("k_rot", _vp),
+        ("stride_b", _i64), ("stride_t", _i64), ("stride_h", _i64),
     ]
 
 

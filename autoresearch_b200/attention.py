@@ -42,9 +42,33 @@ class AttnParams:
     k_rot: Optional[torch.Tensor] = None
 
 
-def _check(t: torch.Tensor, name: str, shape=None, dtype=None, device=None) -> int:
-    if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
-        raise ValueError(f"{name} must be a contiguous CUDA tensor")
+def _layout(q: torch.Tensor):
+    """Element strides (b, t, h) of a [B, T, H, D] tensor for ar_attn_params, or None when it is
+    contiguous.  Accepted besides contiguous tensors: a head range cut out of a wider contiguous
+    [B, T, H_all, D] tensor, i.e. strides (T * H_all * D, H_all * D, D, 1)."""
+    if q.is_contiguous():
+        return None
+    sb, st, sh, sd = q.stride()
+    D = q.shape[3]
+    if sd != 1 or sh != D or st % D != 0 or sb % D != 0 or st < q.shape[2] * D or sb < q.shape[1] * st:
+        raise ValueError(f"unsupported strides {q.stride()}: only a head range of a contiguous [B,T,H,D] tensor")
+    return (sb, st, sh)
+
+
+def _check(t: torch.Tensor, name: str, shape=None, dtype=None, device=None, layout=None) -> int:
+    """layout: None = must be contiguous; else the (b, t, h) element strides every [B,T,H,D] tensor of
+    the call shares (a [B,T,H] tensor has them divided by D)."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if layout is None:
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    else:
+        D = layout[2]
+        want = (layout[0], layout[1], D, 1) if t.dim() == 4 else (layout[0] // D, layout[1] // D, 1)
+        if tuple(t.stride()) != want:
+            raise ValueError(f"{name} has strides {tuple(t.stride())}, expected {want} (all tensors of a call share "
+                             "one layout)")
     if device is not None and t.device != device:
         raise ValueError(f"{name} is on {t.device}, expected {device} (all tensors of a call share one device)")
     if shape is not None and tuple(t.shape) != tuple(shape):
@@ -52,6 +76,15 @@ def _check(t: torch.Tensor, name: str, shape=None, dtype=None, device=None) -> i
     if dtype is not None and t.dtype != dtype:
         raise ValueError(f"{name} has dtype {t.dtype}, expected {dtype}")
     return t.data_ptr()
+
+
+def _new(shape, dtype, device, layout):
+    """An output tensor in the call's layout (contiguous, or the same cut of a wider tensor)."""
+    if layout is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    D = layout[2]
+    strides = (layout[0], layout[1], D, 1) if len(shape) == 4 else (layout[0] // D, layout[1] // D, 1)
+    return torch.empty_strided(shape, strides, dtype=dtype, device=device)
 
 
 def _workspace(c: "_lib.ArAttnParams", which_pass: int, device) -> Optional[torch.Tensor]:
@@ -109,11 +142,14 @@ def _c_params(p: AttnParams, q: torch.Tensor) -> _lib.ArAttnParams:
         c.rope_mode = 0
     if (p.q_rot is None) != (p.k_rot is None):
         raise ValueError("q_rot and k_rot must be given together")
+    lay = _layout(q)
+    if lay is not None:
+        c.stride_b, c.stride_t, c.stride_h = lay
     if p.q_rot is not None:
         if p.rope is None:
             raise ValueError("q_rot / k_rot need rope tables")
-        c.q_rot = _check(p.q_rot, "q_rot", tuple(q.shape), torch.bfloat16, q.device)
-        c.k_rot = _check(p.k_rot, "k_rot", tuple(q.shape), torch.bfloat16, q.device)
+        c.q_rot = _check(p.q_rot, "q_rot", tuple(q.shape), torch.bfloat16, q.device, lay)
+        c.k_rot = _check(p.k_rot, "k_rot", tuple(q.shape), torch.bfloat16, q.device, lay)
     c.workspace = None
     c.workspace_bytes = 0
     c.stream = p.stream if p.stream is not None else torch.cuda.current_stream(q.device).cuda_stream
@@ -123,13 +159,13 @@ def _c_params(p: AttnParams, q: torch.Tensor) -> _lib.ArAttnParams:
 def attn_fwd(q, k, v, params: AttnParams, out=None, lse=None):
     """Returns (o [B,T,H,D] in q's dtype, lse [B,T,H] fp32)."""
     c = _c_params(params, q)
-    shape, dev = tuple(q.shape), q.device
+    shape, dev, lay = tuple(q.shape), q.device, _layout(q)
     if out is None:
-        out = torch.empty_like(q)
+        out = _new(shape, q.dtype, dev, lay)
     if lse is None:
-        lse = torch.empty(shape[:3], dtype=torch.float32, device=dev)
-    args = (_check(q, "q"), _check(k, "k", shape, q.dtype, dev), _check(v, "v", shape, q.dtype, dev),
-            _check(out, "out", shape, q.dtype, dev), _check(lse, "lse", shape[:3], torch.float32, dev))
+        lse = _new(shape[:3], torch.float32, dev, lay)
+    args = (_check(q, "q", layout=lay), _check(k, "k", shape, q.dtype, dev, lay), _check(v, "v", shape, q.dtype, dev, lay),
+            _check(out, "out", shape, q.dtype, dev, lay), _check(lse, "lse", shape[:3], torch.float32, dev, lay))
     # the library works on the CURRENT device (status word, launches): make it the tensors' device
     with torch.cuda.device(dev):
         ws = _workspace(c, 0, dev)
@@ -141,17 +177,17 @@ def attn_fwd(q, k, v, params: AttnParams, out=None, lse=None):
 def attn_bwd(q, k, v, o, d_o, lse, params: AttnParams, d_buf=None, dq=None, dk=None, dv=None):
     """Returns (dq, dk, dv, d_buf)."""
     c = _c_params(params, q)
-    shape, dev = tuple(q.shape), q.device
+    shape, dev, lay = tuple(q.shape), q.device, _layout(q)
     gd = params.grad_dtype
     if d_buf is None:
-        d_buf = torch.empty(shape[:3], dtype=torch.float32, device=dev)
-    dq = torch.empty(shape, dtype=gd, device=dev) if dq is None else dq
-    dk = torch.empty(shape, dtype=gd, device=dev) if dk is None else dk
-    dv = torch.empty(shape, dtype=gd, device=dev) if dv is None else dv
-    args = (_check(q, "q"), _check(k, "k", shape, q.dtype, dev), _check(v, "v", shape, q.dtype, dev),
-            _check(o, "o", shape, q.dtype, dev), _check(d_o, "d_o", shape, q.dtype, dev),
-            _check(lse, "lse", shape[:3], torch.float32, dev), _check(d_buf, "d_buf", shape[:3], torch.float32, dev),
-            _check(dq, "dq", shape, gd, dev), _check(dk, "dk", shape, gd, dev), _check(dv, "dv", shape, gd, dev))
+        d_buf = _new(shape[:3], torch.float32, dev, lay)
+    dq = _new(shape, gd, dev, lay) if dq is None else dq
+    dk = _new(shape, gd, dev, lay) if dk is None else dk
+    dv = _new(shape, gd, dev, lay) if dv is None else dv
+    args = (_check(q, "q", layout=lay), _check(k, "k", shape, q.dtype, dev, lay), _check(v, "v", shape, q.dtype, dev, lay),
+            _check(o, "o", shape, q.dtype, dev, lay), _check(d_o, "d_o", shape, q.dtype, dev, lay),
+            _check(lse, "lse", shape[:3], torch.float32, dev, lay), _check(d_buf, "d_buf", shape[:3], torch.float32, dev, lay),
+            _check(dq, "dq", shape, gd, dev, lay), _check(dk, "dk", shape, gd, dev, lay), _check(dv, "dv", shape, gd, dev, lay))
     with torch.cuda.device(dev):
         ws = _workspace(c, 1, dev)
         _lib.check(_lib.lib().ar_attn_bwd(ctypes.byref(c), *args))

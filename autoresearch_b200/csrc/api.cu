@@ -115,9 +115,13 @@ static int norm_window(int64_t window, int64_t T) {
 struct Maps {
   CUtensorMap q, k, v, d_o;
 };
-static ar_status make_map(CUtensorMap* m, const void* base, int64_t B, int64_t T, int64_t H,
-                          int box_rows = kTile) {
-  if (!make_tmap_bthd(m, base, B, T, H, kHeadDim, box_rows))
+// Layout of the caller's tensors in rows of head_dim elements (see AttnDims); {0, 0} = contiguous.
+struct Layout {
+  int64_t pitch_t = 0, pitch_b = 0;
+};
+static ar_status make_map(CUtensorMap* m, const void* base, int64_t B, int64_t T, int64_t H, int box_rows,
+                          const Layout& lay) {
+  if (!make_tmap_bthd(m, base, B, T, H, kHeadDim, box_rows, lay.pitch_t, lay.pitch_b))
     return fail(AR_ERR_CUDA, "cuTensorMapEncodeTiled failed (driver entry point missing or bad tensor)");
   return AR_OK;
 }
@@ -140,16 +144,24 @@ static ar_status finish(DeviceState* st, uint32_t flags, cudaStream_t stream) {
 }
 
 // ---- core drivers on bf16 operands ---------------------------------------------------------
+static AttnDims make_dims(int64_t B, int64_t T, int64_t H, int window, const Layout& lay) {
+  const int64_t pt = lay.pitch_t ? lay.pitch_t : H;
+  return AttnDims{(int)B, (int)T, (int)H, window, (int)pt, (long long)(lay.pitch_b ? lay.pitch_b : T * pt)};
+}
+
+// `lay` is the layout of o and lse and of those of q, k, v whose flag in `caller` (bit 0: q, 1: k,
+// 2: v) is set; the others are contiguous scratch.
 static ar_status run_fwd(DeviceState* st, const __nv_bfloat16* q, const __nv_bfloat16* k,
                          const __nv_bfloat16* v, void* o, int o_f32, float* lse, int64_t B, int64_t T,
                          int64_t H, int window, const float* cos_buf, const float* sin_buf,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const Layout& lay = Layout(), unsigned caller = 0) {
   Maps m;
-  AR_TRY(make_map(&m.q, q, B, T, H));
-  AR_TRY(make_map(&m.k, k, B, T, H));
-  AR_TRY(make_map(&m.v, v, B, T, H));
+  const Layout contig;
+  AR_TRY(make_map(&m.q, q, B, T, H, kTile, (caller & 1u) ? lay : contig));
+  AR_TRY(make_map(&m.k, k, B, T, H, kTile, (caller & 2u) ? lay : contig));
+  AR_TRY(make_map(&m.v, v, B, T, H, kTile, (caller & 4u) ? lay : contig));
   FwdParams p;
-  p.dims = AttnDims{(int)B, (int)T, (int)H, window};
+  p.dims = make_dims(B, T, H, window, lay);
   p.scale = 1.0f / sqrtf((float)kHeadDim);
   p.scale_log2e = p.scale * kLog2e;
   p.o = o;
@@ -166,14 +178,18 @@ static ar_status run_bwd(DeviceState* st, bool want_dq, bool want_dkv, const __n
                          const __nv_bfloat16* k, const __nv_bfloat16* v, const __nv_bfloat16* d_o,
                          const float* lse, const float* d_buf, const __nv_bfloat16* o_for_d, float* d_out, void* stats_ws,
                          void* dq, void* dk, void* dv, int grad_f32, int64_t B, int64_t T, int64_t H, int window,
-                         const float* cos_buf, const float* sin_buf, cudaStream_t stream) {
+                         const float* cos_buf, const float* sin_buf, cudaStream_t stream,
+                         const Layout& lay = Layout(), unsigned caller = 0) {
+  // `lay`: layout of lse, d_buf, o_for_d, the gradients, and of those of q, k, v, d_o whose flag in
+  // `caller` (bit 0: q, 1: k, 2: v, 3: d_o) is set; the others are contiguous scratch.
   Maps m;   // the backward kernels move every operand in 64-row boxes
-  AR_TRY(make_map(&m.q, q, B, T, H, 64));
-  AR_TRY(make_map(&m.k, k, B, T, H, 64));
-  AR_TRY(make_map(&m.v, v, B, T, H, 64));
-  AR_TRY(make_map(&m.d_o, d_o, B, T, H, 64));
+  const Layout contig;
+  AR_TRY(make_map(&m.q, q, B, T, H, 64, (caller & 1u) ? lay : contig));
+  AR_TRY(make_map(&m.k, k, B, T, H, 64, (caller & 2u) ? lay : contig));
+  AR_TRY(make_map(&m.v, v, B, T, H, 64, (caller & 4u) ? lay : contig));
+  AR_TRY(make_map(&m.d_o, d_o, B, T, H, 64, (caller & 8u) ? lay : contig));
   BwdParams p;
-  p.dims = AttnDims{(int)B, (int)T, (int)H, window};
+  p.dims = make_dims(B, T, H, window, lay);
   p.scale = 1.0f / sqrtf((float)kHeadDim);
   p.scale_log2e = p.scale * kLog2e;
   p.lse = lse;
@@ -191,7 +207,8 @@ static ar_status run_bwd(DeviceState* st, bool want_dq, bool want_dkv, const __n
   p.lse2_t_out = lse2_t;
   p.dvec_t_out = dvec_t;
   if (want_dkv && !o_for_d)
-    AR_CUDA(launch_stats_transpose(lse2_t, dvec_t, lse, d_buf, (int)B, (int)T, (int)H, p.t_pad, stream),
+    AR_CUDA(launch_stats_transpose(lse2_t, dvec_t, lse, d_buf, (int)B, (int)T, (int)H, p.t_pad, stream,
+                                   RowMap{(int)T, (int)H, p.dims.pitch_t, p.dims.pitch_b}),
             "stats transpose launch");
   p.dq = dq;
   p.dk = dk;
@@ -517,12 +534,35 @@ static ar_status check_params(const ar_attn_params* p) {
     if (!aligned16(p->cos_buf) || !aligned16(p->sin_buf))
       return fail(AR_ERR_BAD_ARG, "rope tables must be 16-byte aligned");
   }
+  if (p->stride_b != 0 || p->stride_t != 0 || p->stride_h != 0) {
+    if (p->stride_h != p->D)
+      return fail(AR_ERR_UNSUPPORTED, "stride_h must equal head_dim (the heads of one token adjacent)");
+    if (p->stride_t % p->D != 0 || p->stride_t < p->H * p->D)
+      return fail(AR_ERR_BAD_ARG, "stride_t must be a multiple of head_dim and at least H * head_dim");
+    if (p->stride_b % p->D != 0 || p->stride_b < p->T * p->stride_t)
+      return fail(AR_ERR_BAD_ARG, "stride_b must be a multiple of head_dim and at least T * stride_t");
+  }
   if ((p->q_rot == nullptr) != (p->k_rot == nullptr))
     return fail(AR_ERR_BAD_ARG, "q_rot and k_rot must be given together");
   if (p->q_rot && p->rope_mode != 1) return fail(AR_ERR_BAD_ARG, "q_rot / k_rot need rope_mode 1");
   if (p->q_rot && (!aligned16(p->q_rot) || !aligned16(p->k_rot)))
     return fail(AR_ERR_BAD_ARG, "q_rot / k_rot must be 16-byte aligned");
   return AR_OK;
+}
+
+// The caller's layout from the stride fields (all zero: contiguous), and the row map of a helper
+// kernel's tensor in that layout.
+static Layout layout_of(const ar_attn_params* p) {
+  Layout lay;
+  if (p->stride_t != 0) {
+    lay.pitch_t = p->stride_t / p->D;
+    lay.pitch_b = p->stride_b / p->D;
+  }
+  return lay;
+}
+static RowMap row_map(const ar_attn_params* p, const Layout& lay) {
+  if (lay.pitch_t == 0) return RowMap();
+  return RowMap{(int)p->T, (int)p->H, (int)lay.pitch_t, (long long)lay.pitch_b};
 }
 
 // Scratch layout: `count` bf16 tensors of n elements, each 1024-byte aligned.
@@ -578,6 +618,10 @@ AR_API ar_status ar_attn_fwd(const ar_attn_params* p, const void* q, const void*
   const long long rows = p->B * p->T * p->H;
   const int H = (int)p->H;
   const bool rope = p->rope_mode == 1;
+  const Layout lay = layout_of(p);
+  const RowMap cm = row_map(p, lay), none;   // caller's tensors / contiguous scratch
+  const RowMap rot_map = p->q_rot ? cm : none;   // q_rot, k_rot share the caller's layout
+  unsigned caller = 0;                       // which of q, k, v the attention kernel reads in the caller's layout
   const __nv_bfloat16 *qb, *kb, *vb;
   const float *fc = nullptr, *fs = nullptr;  // tables handed to the attention kernel (fused rope)
   if (p->io_dtype == AR_F32) {
@@ -586,24 +630,27 @@ AR_API ar_status ar_attn_fwd(const ar_attn_params* p, const void* q, const void*
                         : reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + each);
     auto* b2 = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + 2 * each);
     const int mode = rope ? kRopeFwd : kCastOnly;  // staging pass rotates while it casts
-    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b0, (const float*)q, p->cos_buf, p->sin_buf, rows, H, 128, p->T, mode, s)), "stage q");
-    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b1, (const float*)k, p->cos_buf, p->sin_buf, rows, H, 128, p->T, mode, s)), "stage k");
-    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b2, (const float*)v, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s)), "stage v");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b0, (const float*)q, p->cos_buf, p->sin_buf, rows, H, 128, p->T, mode, s, cm, rot_map)), "stage q");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b1, (const float*)k, p->cos_buf, p->sin_buf, rows, H, 128, p->T, mode, s, cm, rot_map)), "stage k");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b2, (const float*)v, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s, cm, none)), "stage v");
     qb = b0; kb = b1; vb = b2;
+    if (p->q_rot) caller |= 3u;
   } else {
     qb = (const __nv_bfloat16*)q; kb = (const __nv_bfloat16*)k; vb = (const __nv_bfloat16*)v;
+    caller = 7u;
     if (rope && ((p->flags & AR_FLAG_ROPE_PREPASS) || p->q_rot)) {
       auto* b0 = p->q_rot ? static_cast<__nv_bfloat16*>(p->q_rot) : reinterpret_cast<__nv_bfloat16*>(ws);
       auto* b1 = p->k_rot ? static_cast<__nv_bfloat16*>(p->k_rot)
                           : reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + each);
-      AR_CUDA(launch_rope_pair_bf16_128(b0, qb, b1, kb, p->cos_buf, p->sin_buf, rows / H, H, p->T, s), "rope q, k");
+      AR_CUDA(launch_rope_pair_bf16_128(b0, qb, b1, kb, p->cos_buf, p->sin_buf, rows / H, H, p->T, s, cm, rot_map), "rope q, k");
       qb = b0; kb = b1;
+      if (!p->q_rot) caller = 4u;
     } else if (rope) {
       fc = p->cos_buf; fs = p->sin_buf;
     }
   }
   AR_TRY(run_fwd(st, qb, kb, vb, o, p->io_dtype == AR_F32, lse, p->B, p->T, p->H,
-                 norm_window(p->window, p->T), fc, fs, s));
+                 norm_window(p->window, p->T), fc, fs, s, lay, caller));
   return finish(st, p->flags, s);
 }
 
@@ -632,41 +679,47 @@ AR_API ar_status ar_attn_bwd(const ar_attn_params* p, const void* q, const void*
   const int H = (int)p->H;
   const bool rope = p->rope_mode == 1;
   const int rmode = rope ? kRopeFwd : kCastOnly;
+  const Layout lay = layout_of(p);
+  const RowMap cm = row_map(p, lay), none;   // caller's tensors / contiguous scratch
+  unsigned caller = 0;                       // which of q, k, v, dO the kernels read in the caller's layout
   const __nv_bfloat16 *qb, *kb, *vb, *dob;
   const __nv_bfloat16* o_for_d = nullptr;
   if (p->io_dtype == AR_F32) {
-    if (do_d) AR_CUDA(launch_precompute_d<float>(d_buf, (const float*)o, (const float*)d_o, rows, 128, s), "precompute_d");
+    if (do_d) AR_CUDA(launch_precompute_d<float>(d_buf, (const float*)o, (const float*)d_o, rows, 128, s, cm), "precompute_d");
     __nv_bfloat16* b[4];
     for (int i = 0; i < 4; ++i) b[i] = reinterpret_cast<__nv_bfloat16*>(tens + i * each);
     if (p->q_rot) {   // rotated and staged by the forward pass
       b[0] = static_cast<__nv_bfloat16*>(p->q_rot);
       b[1] = static_cast<__nv_bfloat16*>(p->k_rot);
+      caller |= 3u;
     } else {
-      AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[0], (const float*)q, p->cos_buf, p->sin_buf, rows, H, 128, p->T, rmode, s)), "stage q");
-      AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[1], (const float*)k, p->cos_buf, p->sin_buf, rows, H, 128, p->T, rmode, s)), "stage k");
+      AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[0], (const float*)q, p->cos_buf, p->sin_buf, rows, H, 128, p->T, rmode, s, cm, none)), "stage q");
+      AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[1], (const float*)k, p->cos_buf, p->sin_buf, rows, H, 128, p->T, rmode, s, cm, none)), "stage k");
     }
-    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[2], (const float*)v, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s)), "stage v");
-    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[3], (const float*)d_o, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s)), "stage dO");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[2], (const float*)v, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s, cm, none)), "stage v");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(b[3], (const float*)d_o, nullptr, nullptr, rows, H, 128, 0, kCastOnly, s, cm, none)), "stage dO");
     qb = b[0]; kb = b[1]; vb = b[2]; dob = b[3];
   } else {
     // D rides along in the dQ kernel when both are wanted (it holds the dO tile anyway)
     if (do_d && do_dq) o_for_d = (const __nv_bfloat16*)o;
-    else if (do_d) AR_CUDA(launch_precompute_d<__nv_bfloat16>(d_buf, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, rows, 128, s), "precompute_d");
+    else if (do_d) AR_CUDA(launch_precompute_d<__nv_bfloat16>(d_buf, (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, rows, 128, s, cm), "precompute_d");
     qb = (const __nv_bfloat16*)q; kb = (const __nv_bfloat16*)k;
     vb = (const __nv_bfloat16*)v; dob = (const __nv_bfloat16*)d_o;
+    caller = 15u;
     if (rope && p->q_rot) {
       qb = static_cast<const __nv_bfloat16*>(p->q_rot);   // rotated in the forward pass
       kb = static_cast<const __nv_bfloat16*>(p->k_rot);
     } else if (rope) {
       auto* b0 = reinterpret_cast<__nv_bfloat16*>(tens);
       auto* b1 = reinterpret_cast<__nv_bfloat16*>(tens + each);
-      AR_CUDA(launch_rope_pair_bf16_128(b0, qb, b1, kb, p->cos_buf, p->sin_buf, rows / H, H, p->T, s), "rope q, k");
+      AR_CUDA(launch_rope_pair_bf16_128(b0, qb, b1, kb, p->cos_buf, p->sin_buf, rows / H, H, p->T, s, cm, none), "rope q, k");
       qb = b0; kb = b1;
+      caller = 12u;
     }
   }
   AR_TRY(run_bwd(st, do_dq, do_dkv, qb, kb, vb, dob, lse, d_buf, o_for_d, d_buf, ws, dq, dk, dv, p->grad_dtype == AR_F32,
                  p->B, p->T, p->H, norm_window(p->window, p->T), rope ? p->cos_buf : nullptr,
-                 rope ? p->sin_buf : nullptr, s));
+                 rope ? p->sin_buf : nullptr, s, lay, caller));
   return finish(st, p->flags, s);
 }
 

@@ -369,10 +369,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       tc_fence_before();
       mbar_arrive(smem_u32(&sm.acc_free));
       const int esize = p.grad_f32 ? 4 : 2;
-      const size_t row_stride = (size_t)H * 128 * esize;
+      const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
       const int wrow0 = row0 + 32 * (warp & 3);   // first row of this warp's 32-row block
       uint8_t* gout = static_cast<uint8_t*>(wg == 0 ? p.dv : p.dk) +
-                      (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
+                      row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
       const int rows_valid = T - wrow0;
       const float mul = wg == 0 ? 1.f : p.scale * kTruncGainInv;   // dS carried the gain of P'
       const bool rot = wg == 1 && p.cos_buf != nullptr;

@@ -298,7 +298,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int pp = 0; pp < 4; ++pp) {
           const int row_g = di.row0 + 32 * wq + 8 * bt + 2 * pp + half;
           if (row_g < T) {
-            const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
+            const size_t ri = row_of(p.dims, di.b, row_g, di.h);
             ov[pp] = __ldg(reinterpret_cast<const uint4*>(p.o_for_d + ri * 128) + ch);
             dv[pp] = __ldg(reinterpret_cast<const uint4*>(p.do_for_d + ri * 128) + ch);
           } else {
@@ -333,7 +333,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const size_t ti = ((size_t)di.b * H + di.h) * p.t_pad + row_g;
         float addend = -INFINITY;
         if (valid) {
-          const size_t ri = ((size_t)di.b * T + row_g) * H + di.h;
+          const size_t ri = row_of(p.dims, di.b, row_g, di.h);
           p.d_out[ri] = mine;
           addend = kTruncGainLog2 - p.lse[ri] * kLog2e;
         }
@@ -362,7 +362,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const DqItem wi = dq_item(item, p.dims, n_qt);
       const int row0 = wi.row0, row = row0 + r;
       const bool valid = row < T;
-      const size_t row_index = ((size_t)wi.b * T + (size_t)min(row, T - 1)) * H + wi.h;
+      const size_t row_index = row_of(p.dims, wi.b, min(row, T - 1), wi.h);
       // exp(s*scale - lse) = exp2(s*scale*log2e - lse*log2e); rows past T get lse = +inf, i.e. P = 0
       const float lse2 = valid ? p.lse[row_index] * kLog2e : INFINITY;
       float d_row = (!fuse_d && valid) ? p.dvec[row_index] : 0.f;
@@ -472,9 +472,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // transposition buffer of this warp: 2 KB of the V slot that held the item's last V tile
         const uint32_t epi = smem_u32(sm.v[(g - 1) % kDqVStages]) + warp * 2048u;
         const int esize = p.grad_f32 ? 4 : 2;
-        const size_t row_stride = (size_t)H * 128 * esize;
+        const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
         const int wrow0 = row0 + 32 * (warp & 3);
-        uint8_t* gout = static_cast<uint8_t*>(p.dq) + (((size_t)wi.b * T + wrow0) * H + wi.h) * 128 * esize;
+        uint8_t* gout = static_cast<uint8_t*>(p.dq) + row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
         warp_store_32cols(epi, lane, lo_v, gout + (size_t)(wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
         warp_store_32cols(epi, lane, hi_v, gout + (size_t)(64 + wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
         fence_proxy_async_smem();   // the slot is next written by a bulk tensor load

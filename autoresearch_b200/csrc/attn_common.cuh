@@ -14,7 +14,29 @@ constexpr float kLn2 = 0.6931471805599453f;
 struct AttnDims {
   int B, T, H;
   int window;  // normalised: 0 = full causal, else 1 <= window <= T-1 (keys q-window .. q)
+  // Layout of the caller's tensors in rows of head_dim elements: row (b, t, h) is row
+  // b * pitch_b + t * pitch_t + h of q, k, v, o, dO and the gradients, and element
+  // b * pitch_b + t * pitch_t + h of LSE and D.  Contiguous [B,T,H,D]: pitch_t = H, pitch_b = T * H;
+  // a head range cut out of a wider tensor keeps the wider tensor's pitches.
+  int pitch_t;
+  long long pitch_b;
 };
+__host__ __device__ __forceinline__ size_t row_of(const AttnDims& d, int b, int t, int h) {
+  return (size_t)b * (size_t)d.pitch_b + (size_t)t * (size_t)d.pitch_t + (size_t)h;
+}
+
+// How a helper kernel finds row r = (b * T + t) * H + h of one of its tensors: T == 0 means the
+// tensor is contiguous (row r is row r), otherwise the pitches above apply.
+struct RowMap {
+  int T = 0, H = 0, pitch_t = 0;
+  long long pitch_b = 0;
+};
+__host__ __device__ __forceinline__ long long map_row(const RowMap& m, long long r) {
+  if (m.T == 0) return r;
+  const long long token = r / m.H, h = r - token * m.H;
+  const long long b = token / m.T, t = token - b * m.T;
+  return b * m.pitch_b + t * m.pitch_t + h;
+}
 
 
 // ---- kernel parameter blocks and launchers (definitions in attn_fwd.cu / attn_bwd.cu /
@@ -67,11 +89,12 @@ cudaError_t launch_attn_bwd_dkv(const CUtensorMap& mq, const CUtensorMap& mk, co
 template <typename InT, typename OutT>
 cudaError_t launch_rope_cast(OutT* out, const InT* in, const float* cos_buf, const float* sin_buf,
                              long long rows, int num_heads, int head_dim, long long seq_len,
-                             int mode, cudaStream_t stream);
+                             int mode, cudaStream_t stream, RowMap in_map = RowMap(), RowMap out_map = RowMap());
 // Forward rotation of bf16 Q and K ([tokens, H, 128] each) in one launch.
 cudaError_t launch_rope_pair_bf16_128(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bfloat16* out1,
                                       const __nv_bfloat16* in1, const float* cos_buf, const float* sin_buf,
-                                      long long tokens, int num_heads, long long seq_len, cudaStream_t stream);
+                                      long long tokens, int num_heads, long long seq_len, cudaStream_t stream,
+                                      RowMap in_map = RowMap(), RowMap out_map = RowMap());
 // rope_fwd + per-head rmsnorm_fwd on q, k and the bf16 cast of q, k, v in one launch (head_dim 128);
 // v / v_out may be null (q and k only); rms_q / rms_k may be null.
 template <typename InT>
@@ -84,10 +107,10 @@ cudaError_t launch_rope_scalar(float* out, const float* in, const float* cos_buf
                                long long seq_len, int mode, cudaStream_t stream);
 template <typename T>
 cudaError_t launch_precompute_d(float* d_out, const T* o, const T* d_o, long long rows, int head_dim,
-                                cudaStream_t stream);
+                                cudaStream_t stream, RowMap map = RowMap());
 // [B,T,H] LSE and D -> key-stationary layout [B,H,Tp]: LSE * log2(e) (pad +inf) and D (pad 0).
 cudaError_t launch_stats_transpose(float* lse2_t, float* dvec_t, const float* lse, const float* dvec,
-                                   int B, int T, int H, int t_pad, cudaStream_t stream);
+                                   int B, int T, int H, int t_pad, cudaStream_t stream, RowMap map = RowMap());
 
 // Launches a persistent kernel with programmatic stream serialization allowed (see ptx.cuh).
 template <typename... KArgs, typename... Args>

@@ -336,9 +336,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float inv_l = 1.f / l_run;
       {
         const int esize = p.o_f32 ? 4 : 2;
-        const size_t row_stride = (size_t)p.dims.H * 128 * esize;
+        const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
         const int wrow0 = qlo + 32 * (warp & 3);   // first row of this warp's 32-row block
-        uint8_t* gout = static_cast<uint8_t*>(p.o) + (((size_t)wi.b * T + wrow0) * p.dims.H + wi.h) * 128 * esize;
+        uint8_t* gout = static_cast<uint8_t*>(p.o) + row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
         const uint32_t wbase = epi + lane * 128u;
         const uint32_t sw = lane & 7u;
         if (p.o_f32) {
@@ -373,7 +373,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
       }
-      if (qrow < T) p.lse[((size_t)wi.b * T + qrow) * p.dims.H + wi.h] = m_ref * p.scale + logf(l_run);
+      if (qrow < T) p.lse[row_of(p.dims, wi.b, qrow, wi.h)] = m_ref * p.scale + logf(l_run);
       g_own += n_it;
       g_oth += n_other;
       ++nx;
@@ -572,9 +572,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const uint32_t tO = tmem + 256 + X * 128 + lane_off;
           const int qlo = wi.q0 + kTile * X, qrow = qlo + r;
           const int esize = p.o_f32 ? 4 : 2;
-          const size_t row_stride = (size_t)p.dims.H * 128 * esize;
+          const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
           const int wrow0 = qlo + 32 * wq;   // first row of this warp's 32-row block
-          uint8_t* gout = static_cast<uint8_t*>(p.o) + (((size_t)wi.b * T + wrow0) * p.dims.H + wi.h) * 128 * esize;
+          uint8_t* gout = static_cast<uint8_t*>(p.o) + row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t og[32];
@@ -613,7 +613,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               }
             }
           }
-          if (qrow < T) p.lse[((size_t)wi.b * T + qrow) * p.dims.H + wi.h] = m_row * p.scale + logf(l_row);
+          if (qrow < T) p.lse[row_of(p.dims, wi.b, qrow, wi.h)] = m_row * p.scale + logf(l_row);
           if (X == 0) ++nxe[0]; else ++nxe[1];
         }
       }

@@ -37,14 +37,15 @@ template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
 rope_cast_kernel(OutT* out, const InT* in, const float* __restrict__ cos_buf,
                  const float* __restrict__ sin_buf, long long rows, int num_heads, int half,
-                 long long seq_len, int mode) {
+                 long long seq_len, int mode, const RowMap in_map, const RowMap out_map) {
   const int groups = half >> 2;
   const long long total = rows * groups;
   for (long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x; tid < total;
        tid += (long long)gridDim.x * blockDim.x) {
     const long long row = tid / groups;
     const int g = static_cast<int>(tid - row * groups);
-    const long long base = row * 2 * half + g * 4;
+    const long long base = map_row(in_map, row) * 2 * half + g * 4;
+    const long long obase = map_row(out_map, row) * 2 * half + g * 4;
     float4 x1 = Vec4<InT>::load(in + base);
     float4 x2 = Vec4<InT>::load(in + base + half);
     if (mode != kCastOnly) {
@@ -61,8 +62,8 @@ rope_cast_kernel(OutT* out, const InT* in, const float* __restrict__ cos_buf,
       x1 = y1;
       x2 = y2;
     }
-    Vec4<OutT>::store(out + base, x1);
-    Vec4<OutT>::store(out + base + half, x2);
+    Vec4<OutT>::store(out + obase, x1);
+    Vec4<OutT>::store(out + obase + half, x2);
   }
 }
 
@@ -73,7 +74,8 @@ rope_cast_kernel(OutT* out, const InT* in, const float* __restrict__ cos_buf,
 __global__ void __launch_bounds__(256)
 rope_pair_bf16_128_kernel(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bfloat16* out1,
                           const __nv_bfloat16* in1, const float* __restrict__ cos_buf,
-                          const float* __restrict__ sin_buf, long long tokens, int num_heads, long long seq_len) {
+                          const float* __restrict__ sin_buf, long long tokens, int num_heads, long long seq_len,
+                          const RowMap in_map, const RowMap out_map) {
   const __nv_bfloat16* in = blockIdx.y == 0 ? in0 : in1;
   __nv_bfloat16* out = blockIdx.y == 0 ? out0 : out1;
   const long long total = tokens * 8;
@@ -88,8 +90,9 @@ rope_pair_bf16_128_kernel(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bf
     const float4 s1 = __ldg(reinterpret_cast<const float4*>(sin_buf + pos * 64 + g * 8 + 4));
     const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
     const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const long long irow0 = map_row(in_map, token * num_heads), orow0 = map_row(out_map, token * num_heads);
     for (int h = 0; h < num_heads; ++h) {
-      const long long base = (token * num_heads + h) * 128 + g * 8;
+      const long long base = (irow0 + h) * 128 + g * 8, obase = (orow0 + h) * 128 + g * 8;
       const uint4 a = *reinterpret_cast<const uint4*>(in + base);
       const uint4 b = *reinterpret_cast<const uint4*>(in + base + 64);
       const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -102,8 +105,8 @@ rope_pair_bf16_128_kernel(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bf
         ya[i] = pack_bf16x2(x1l * cs[2 * i] + x2l * sn[2 * i], x1h * cs[2 * i + 1] + x2h * sn[2 * i + 1]);
         yb[i] = pack_bf16x2(x2l * cs[2 * i] - x1l * sn[2 * i], x2h * cs[2 * i + 1] - x1h * sn[2 * i + 1]);
       }
-      *reinterpret_cast<uint4*>(out + base) = make_uint4(ya[0], ya[1], ya[2], ya[3]);
-      *reinterpret_cast<uint4*>(out + base + 64) = make_uint4(yb[0], yb[1], yb[2], yb[3]);
+      *reinterpret_cast<uint4*>(out + obase) = make_uint4(ya[0], ya[1], ya[2], ya[3]);
+      *reinterpret_cast<uint4*>(out + obase + 64) = make_uint4(yb[0], yb[1], yb[2], yb[3]);
     }
   }
 }
@@ -224,30 +227,31 @@ static int grid_for(long long total, int block) {
 template <typename InT, typename OutT>
 cudaError_t launch_rope_cast(OutT* out, const InT* in, const float* cos_buf, const float* sin_buf,
                              long long rows, int num_heads, int head_dim, long long seq_len,
-                             int mode, cudaStream_t stream) {
+                             int mode, cudaStream_t stream, RowMap in_map, RowMap out_map) {
   const int half = head_dim / 2;
   const long long total = rows * (half >> 2);
   rope_cast_kernel<InT, OutT><<<grid_for(total, 256), 256, 0, stream>>>(
-      out, in, cos_buf, sin_buf, rows, num_heads, half, seq_len, mode);
+      out, in, cos_buf, sin_buf, rows, num_heads, half, seq_len, mode, in_map, out_map);
   return cudaGetLastError();
 }
 cudaError_t launch_rope_pair_bf16_128(__nv_bfloat16* out0, const __nv_bfloat16* in0, __nv_bfloat16* out1,
                                       const __nv_bfloat16* in1, const float* cos_buf, const float* sin_buf,
-                                      long long tokens, int num_heads, long long seq_len, cudaStream_t stream) {
+                                      long long tokens, int num_heads, long long seq_len, cudaStream_t stream,
+                                      RowMap in_map, RowMap out_map) {
   dim3 grid(grid_for(tokens * 8, 256), 2);
   rope_pair_bf16_128_kernel<<<grid, 256, 0, stream>>>(out0, in0, out1, in1, cos_buf, sin_buf, tokens, num_heads,
-                                                      seq_len);
+                                                      seq_len, in_map, out_map);
   return cudaGetLastError();
 }
 template cudaError_t launch_rope_cast<float, float>(float*, const float*, const float*, const float*,
-                                                    long long, int, int, long long, int, cudaStream_t);
+                                                    long long, int, int, long long, int, cudaStream_t, RowMap, RowMap);
 template cudaError_t launch_rope_cast<float, __nv_bfloat16>(__nv_bfloat16*, const float*, const float*,
                                                             const float*, long long, int, int,
-                                                            long long, int, cudaStream_t);
+                                                            long long, int, cudaStream_t, RowMap, RowMap);
 template cudaError_t launch_rope_cast<__nv_bfloat16, __nv_bfloat16>(__nv_bfloat16*, const __nv_bfloat16*,
                                                                     const float*, const float*,
                                                                     long long, int, int, long long,
-                                                                    int, cudaStream_t);
+                                                                    int, cudaStream_t, RowMap, RowMap);
 
 cudaError_t launch_rope_scalar(float* out, const float* in, const float* cos_buf,
                                const float* sin_buf, long long rows, int num_heads, int head_dim,
@@ -264,7 +268,7 @@ cudaError_t launch_rope_scalar(float* out, const float* in, const float* cos_buf
 template <typename T>
 __global__ void __launch_bounds__(256)
 precompute_d128_kernel(float* __restrict__ d_out, const T* __restrict__ o, const T* __restrict__ d_o,
-                       long long rows) {
+                       long long rows, const RowMap map) {
   constexpr int kPer = 16 / sizeof(T);       // elements per thread: 8 bf16 or 4 fp32
   constexpr int kLanes = 128 / kPer;         // threads per row: 16 or 32
   const long long tid0 = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -276,9 +280,10 @@ precompute_d128_kernel(float* __restrict__ d_out, const T* __restrict__ o, const
   for (long long i = 0; i < n_iter; ++i) {
     const long long row = tid0 / kLanes + i * rows_per_sweep;
     float acc = 0.f;
+    const long long mrow = row < rows ? map_row(map, row) : 0;
     if (row < rows) {
-      const uint4 a = *reinterpret_cast<const uint4*>(o + row * 128 + seg * kPer);
-      const uint4 g = *reinterpret_cast<const uint4*>(d_o + row * 128 + seg * kPer);
+      const uint4 a = *reinterpret_cast<const uint4*>(o + mrow * 128 + seg * kPer);
+      const uint4 g = *reinterpret_cast<const uint4*>(d_o + mrow * 128 + seg * kPer);
       const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -290,7 +295,7 @@ precompute_d128_kernel(float* __restrict__ d_out, const T* __restrict__ o, const
     }
 #pragma unroll
     for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (seg == 0 && row < rows) d_out[row] = acc;
+    if (seg == 0 && row < rows) d_out[mrow] = acc;
   }
 }
 
@@ -298,50 +303,51 @@ precompute_d128_kernel(float* __restrict__ d_out, const T* __restrict__ o, const
 template <typename T>
 __global__ void __launch_bounds__(256)
 precompute_d_kernel(float* __restrict__ d_out, const T* __restrict__ o, const T* __restrict__ d_o,
-                    long long rows, int head_dim) {
+                    long long rows, int head_dim, const RowMap map) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   for (long long row = warp0; row < rows; row += nwarps) {
+    const long long mrow = map_row(map, row);
     float acc = 0.f;
     for (int d = lane * 4; d < head_dim; d += 128) {
-      const float4 a = Vec4<T>::load(o + row * head_dim + d);
-      const float4 g = Vec4<T>::load(d_o + row * head_dim + d);
+      const float4 a = Vec4<T>::load(o + mrow * head_dim + d);
+      const float4 g = Vec4<T>::load(d_o + mrow * head_dim + d);
       acc += a.x * g.x + a.y * g.y + a.z * g.z + a.w * g.w;
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) d_out[row] = acc;
+    if (lane == 0) d_out[mrow] = acc;
   }
 }
 
 template <typename T>
 cudaError_t launch_precompute_d(float* d_out, const T* o, const T* d_o, long long rows, int head_dim,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, RowMap map) {
   if (head_dim == 128) {
     constexpr int kLanes = 128 / (16 / (int)sizeof(T));
     const long long threads = rows * kLanes;
     long long blocks = (threads + 255) / 256;
     const long long cap = 148LL * 16;
     if (blocks > cap) blocks = cap;
-    precompute_d128_kernel<T><<<(int)(blocks < 1 ? 1 : blocks), 256, 0, stream>>>(d_out, o, d_o, rows);
+    precompute_d128_kernel<T><<<(int)(blocks < 1 ? 1 : blocks), 256, 0, stream>>>(d_out, o, d_o, rows, map);
   } else {
-    precompute_d_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream>>>(d_out, o, d_o, rows, head_dim);
+    precompute_d_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream>>>(d_out, o, d_o, rows, head_dim, map);
   }
   return cudaGetLastError();
 }
 template cudaError_t launch_precompute_d<float>(float*, const float*, const float*, long long, int,
-                                                cudaStream_t);
+                                                cudaStream_t, RowMap);
 template cudaError_t launch_precompute_d<__nv_bfloat16>(float*, const __nv_bfloat16*,
                                                         const __nv_bfloat16*, long long, int,
-                                                        cudaStream_t);
+                                                        cudaStream_t, RowMap);
 
 
 // One thread per (b, h, tp): gathers LSE and D from [B,T,H] into [B,H,Tp] (coalesced writes).  The LSE
 // is stored as the addend of the dK/dV kernel's exponent: kTruncGainLog2 - LSE * log2(e).
 __global__ void __launch_bounds__(256)
 stats_transpose_kernel(float* __restrict__ lse2_t, float* __restrict__ dvec_t, const float* __restrict__ lse,
-                       const float* __restrict__ dvec, int B, int T, int H, int t_pad) {
+                       const float* __restrict__ dvec, int B, int T, int H, int t_pad, const RowMap map) {
   const long long total = (long long)B * H * t_pad;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -351,7 +357,7 @@ stats_transpose_kernel(float* __restrict__ lse2_t, float* __restrict__ dvec_t, c
     const long long bb = bh / H;
     float l = -INFINITY, d = 0.f;   // padding rows: exponent -inf, P = 0
     if (tp < T) {
-      const long long src = (bb * T + tp) * H + hh;
+      const long long src = map_row(map, (bb * T + tp) * H + hh);
       l = kTruncGainLog2 - lse[src] * kLog2e;
       d = dvec[src];
     }
@@ -361,9 +367,9 @@ stats_transpose_kernel(float* __restrict__ lse2_t, float* __restrict__ dvec_t, c
 }
 
 cudaError_t launch_stats_transpose(float* lse2_t, float* dvec_t, const float* lse, const float* dvec,
-                                   int B, int T, int H, int t_pad, cudaStream_t stream) {
+                                   int B, int T, int H, int t_pad, cudaStream_t stream, RowMap map) {
   stats_transpose_kernel<<<grid_for((long long)B * H * t_pad, 256), 256, 0, stream>>>(lse2_t, dvec_t, lse,
-                                                                                      dvec, B, T, H, t_pad);
+                                                                                      dvec, B, T, H, t_pad, map);
   return cudaGetLastError();
 }
 

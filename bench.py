@@ -377,7 +377,9 @@ def run_gpu(args):
         for L in layers:
             p = ab.AttnParams(window=L["w"], rope=tables, skip_d=True, skip_dq=True, skip_dkv=True)
             rope_only.append(p)
-        rope_ms = timed(lambda: [bwd(L, p) for L, p in zip(layers, rope_only)], reps) / reps
+        rope_fn = lambda: [bwd(L, p) for L, p in zip(layers, rope_only)]    # noqa: E731
+        rope_fn()                                  # first use allocates the scratch
+        rope_ms = timed(rope_fn, 4 * reps) / (4 * reps)
         nbytes = 4 * B * T * H * D * 2 * nl       # 2 tensors read + 2 written, bf16
         kernels["rope_pair_bf16_128"] = {"bound": "hbm", "ms_per_step": round(rope_ms, 4), "launches_per_step": nl,
                                          "achieved": nbytes / (rope_ms * 1e-3) / 1e9, "unit": "GB/s",

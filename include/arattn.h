@@ -210,6 +210,13 @@ typedef struct ar_attn_params {
    * or neither; NULL keeps the self-contained behaviour. */
   void* q_rot;
   void* k_rot;
+  /* Optional strides, in ELEMENTS, of q, k, v, o, d_o, dq, dk, dv, q_rot and k_rot (all the same);
+   * all three zero means contiguous [B,T,H,D].  They let a caller hand over a head range cut out
+   * of a wider [B,T,H_all,D] tensor - e.g. one rank's share when (batch, head) units are split
+   * inside a batch - without copying it: stride_h must be D (the heads of a token adjacent),
+   * stride_t = H_all * D, stride_b = T * stride_t (or more; both multiples of D).  lse and d_buf
+   * are then the matching cut of [B,T,H_all]: element strides stride_b / D, stride_t / D, 1. */
+  int64_t stride_b, stride_t, stride_h;
 } ar_attn_params;
 
 /* Bytes of scratch the given call needs (pass 0 = forward, 1 = backward). */

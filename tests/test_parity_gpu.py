@@ -340,3 +340,54 @@ def test_errors_on_device(cuda_device):
     with pytest.raises(ab.ArattnError) as e:
         ab.attn_fwd(q, q, q, ab.AttnParams(rope=(cos, cos)))   # table shorter than T
     assert e.value.status == _lib.AR_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("dtype_name,flow", [("bfloat16", "fused"), ("bfloat16", "saved"), ("bfloat16", "prepass"),
+                                             ("float32", "fused"), ("float32", "saved")])
+def test_head_range_of_a_wider_tensor_without_copy(cuda_device, dtype_name, flow):
+    """A rank that owns a head range of a batch (shard_units' split inside a batch) hands the library
+    views into the wider [B, T, H_all, D] tensors through the stride fields of ar_attn_params; inputs
+    are read and outputs written in place, the other heads are not touched, and the results equal
+    those of the same heads copied out into contiguous tensors, bit for bit."""
+    import torch
+    dtype = getattr(torch, dtype_name)
+    B, T, H_all, W = 2, 777, 5, 300
+    b0, nb, h0, nh = 0, B, 1, 3                      # heads 1..3 of every batch
+    g = torch.Generator(device="cuda").manual_seed(77)
+    wide = {n: torch.randn(B, T, H_all, 128, device="cuda", generator=g).to(torch.bfloat16).to(dtype) for n in "qkvg"}
+    (cos, sin), dtab = rope_tables(T)
+    sl = (slice(b0, b0 + nb), slice(None), slice(h0, h0 + nh))
+
+    def run(views, outs):
+        q, k, v, do = views
+        p = ab.AttnParams(window=W, rope=dtab, rope_prepass=flow == "prepass",
+                          q_rot=outs.get("q_rot"), k_rot=outs.get("k_rot"))
+        ab.attn_fwd(q, k, v, p, out=outs["o"], lse=outs["lse"])
+        ab.attn_bwd(q, k, v, outs["o"], do, outs["lse"], p, d_buf=outs["d"], dq=outs["dq"], dk=outs["dk"], dv=outs["dv"])
+
+    def outputs(shape4, shape3, make):
+        o = {n: make(shape4, dtype) for n in ("o",)}
+        o.update({n: make(shape4, torch.float32) for n in ("dq", "dk", "dv")})
+        o.update({n: make(shape3, torch.float32) for n in ("lse", "d")})
+        if flow == "saved":
+            o.update({n: make(shape4, torch.bfloat16) for n in ("q_rot", "k_rot")})
+        return o
+
+    # contiguous copies of the head range
+    cont = outputs((nb, T, nh, 128), (nb, T, nh), lambda s, dt: torch.zeros(s, device="cuda", dtype=dt))
+    run([wide[n][sl].contiguous() for n in "qkvg"], cont)
+    # views into wide output tensors pre-filled with a sentinel
+    wide_out = outputs((B, T, H_all, 128), (B, T, H_all), lambda s, dt: torch.full(s, 7.0, device="cuda", dtype=dt))
+    views = {n: t[sl] for n, t in wide_out.items()}
+    assert not views["o"].is_contiguous()
+    run([wide[n][sl] for n in "qkvg"], views)
+    _device_ok()
+    for n in cont:
+        assert torch.equal(views[n], cont[n]), n
+        untouched = torch.ones(H_all, dtype=torch.bool, device="cuda")
+        untouched[h0:h0 + nh] = False
+        assert (wide_out[n][:, :, untouched] == 7.0).all(), f"{n}: heads outside the range were written"
+    # and the head range against the oracle
+    host = [wide[n][sl].float().cpu().numpy() for n in "qkvg"]
+    want = orc.attention_path(*host[:3], host[3], W, rope=(cos, sin))
+    assert_parity(compare({n: cont[n] for n in ("o", "lse", "dq", "dk", "dv")}, want), what=f"head range {dtype_name} {flow}")
