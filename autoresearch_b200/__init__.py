@@ -13,6 +13,9 @@ from .ops import (  # noqa: F401
     flash_attn_bwd_dq,
     flash_attn_bwd_precompute_d,
     flash_attn_fwd,
+    linear_bwd_dw,
+    linear_bwd_dx,
+    linear_fwd,
     rope_bwd,
     rope_fwd,
 )
@@ -22,5 +25,5 @@ from .sharding import shard_units  # noqa: F401
 __all__ = [
     "ROPE_BASE", "GPTConfig", "precompute_rope", "window_size", "ArattnError", "lib", "lib_path",
     "rope_fwd", "rope_bwd", "flash_attn_fwd", "flash_attn_bwd_precompute_d", "flash_attn_bwd_dq",
-    "flash_attn_bwd_dkv", "AttnParams", "attn_fwd", "attn_bwd", "attention", "check_device_status", "shard_units",
+    "flash_attn_bwd_dkv", "linear_fwd", "linear_bwd_dx", "linear_bwd_dw", "AttnParams", "attn_fwd", "attn_bwd", "attention", "check_device_status", "shard_units",
 ]

@@ -65,6 +65,9 @@ SIGNATURES = {
     "ar_flash_attn_bwd_precompute_d": (ctypes.c_int32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "ar_flash_attn_bwd_dq": (ctypes.c_int32, [_vp] * 7 + [_i64] * 5 + [_vp]),
     "ar_flash_attn_bwd_dkv": (ctypes.c_int32, [_vp] * 8 + [_i64] * 5 + [_vp]),
+    "ar_linear_fwd": (ctypes.c_int32, [_vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, ctypes.c_int32, _vp]),
+    "ar_linear_bwd_dx": (ctypes.c_int32, [_vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, ctypes.c_int32, _vp]),
+    "ar_linear_bwd_dw": (ctypes.c_int32, [_vp, _vp, _vp, _i64, _i64, _i64, ctypes.c_int32, _vp]),
     "ar_attn_workspace_bytes": (ctypes.c_uint64, [ctypes.POINTER(ArAttnParams), ctypes.c_int32]),
     "ar_attn_fwd": (ctypes.c_int32, [ctypes.POINTER(ArAttnParams)] + [_vp] * 5),
     "ar_attn_bwd": (ctypes.c_int32, [ctypes.POINTER(ArAttnParams)] + [_vp] * 10),

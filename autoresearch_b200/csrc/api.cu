@@ -513,6 +513,79 @@ AR_API ar_status ar_flash_attn_bwd_dkv(float* grad_k, float* grad_v, const float
                     head_dim, window_size, stream);
 }
 
+// ---- projections ---------------------------------------------------------------------------------
+// mode 0: y[M,N] = x[M,K] w[N,K]^T   mode 1: dx[M,K] = dy[M,N] w[N,K]   mode 2: dw[N,K] += dy[M,N]^T x[M,K]
+static ar_status linear_call(int mode, void* out, const void* a_in, const void* b_in, int64_t M, int64_t N, int64_t K,
+                             int32_t in_dtype, int32_t out_dtype, void* stream) {
+  if (!out || !a_in || !b_in) return fail(AR_ERR_BAD_ARG, "null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(AR_ERR_BAD_ARG, "M, N, K must be positive");
+  if (M > (int64_t(1) << 30) || N > (int64_t(1) << 24) || K > (int64_t(1) << 24))
+    return fail(AR_ERR_UNSUPPORTED, "shape out of range");
+  if (N % 8 != 0 || K % 8 != 0) return fail(AR_ERR_UNSUPPORTED, "N and K must be multiples of 8 (16-byte rows)");
+  const int64_t out_cols = mode == 0 ? N : K;
+  if (out_cols % 32 != 0) return fail(AR_ERR_UNSUPPORTED, "the output's row length (%lld) must be a multiple of 32", (long long)out_cols);
+  if (in_dtype != AR_F32 && in_dtype != AR_BF16) return fail(AR_ERR_UNSUPPORTED, "in_dtype %d unknown", in_dtype);
+  if (out_dtype != AR_F32 && out_dtype != AR_BF16) return fail(AR_ERR_UNSUPPORTED, "out_dtype %d unknown", out_dtype);
+  if (mode == 2 && out_dtype != AR_F32) return fail(AR_ERR_UNSUPPORTED, "dw is accumulated in fp32");
+  if (!aligned16(out) || !aligned16(a_in) || !aligned16(b_in)) return fail(AR_ERR_BAD_ARG, "pointers must be 16-byte aligned");
+  DeviceState* st;
+  AR_TRY(device_state(&st));
+  cudaStream_t s = (cudaStream_t)stream;
+  // operand shapes (rows x inner): mode 0: a = x [M,K], b = w [N,K]; 1: a = dy [M,N], b = w [N,K]; 2: a = dy [M,N], b = x [M,K]
+  const int64_t a_rows = M, a_inner = mode == 0 ? K : N;
+  const int64_t b_rows = mode == 2 ? M : N, b_inner = K;
+  const __nv_bfloat16 *ab = (const __nv_bfloat16*)a_in, *bb = (const __nv_bfloat16*)b_in;
+  if (in_dtype == AR_F32) {   // stage both operands as bf16
+    const size_t na = align_up((size_t)a_rows * a_inner * 2, 1024), nb = align_up((size_t)b_rows * b_inner * 2, 1024);
+    void* ws;
+    AR_TRY(library_workspace(st, na + nb, &ws));
+    auto* sa = reinterpret_cast<__nv_bfloat16*>(ws);
+    auto* sb = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(ws) + na);
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(sa, (const float*)a_in, nullptr, nullptr, a_rows, 1, (int)a_inner, 0, kCastOnly, s)), "stage a");
+    AR_CUDA((launch_rope_cast<float, __nv_bfloat16>(sb, (const float*)b_in, nullptr, nullptr, b_rows, 1, (int)b_inner, 0, kCastOnly, s)), "stage b");
+    ab = sa; bb = sb;
+  }
+  // K-major operands move in boxes of (tile rows) x 64 inner elements, MN-major ones in 64 depth rows x 64
+  CUtensorMap ma, mb;
+  const int a_box = mode == 2 ? 64 : 128, b_box = mode == 0 ? 256 : 64;
+  if (!make_tmap_bthd(&ma, ab, 1, a_rows, 1, a_inner, a_box) || !make_tmap_bthd(&mb, bb, 1, b_rows, 1, b_inner, b_box))
+    return fail(AR_ERR_CUDA, "cuTensorMapEncodeTiled failed (driver entry point missing or bad tensor)");
+  LinParams p;
+  p.mode = mode;
+  p.rows_a = (int)(mode == 2 ? N : M);
+  p.cols_b = (int)out_cols;
+  p.depth = (int)(mode == 0 ? K : (mode == 1 ? N : M));
+  p.depth_chunk = (p.depth + 63) / 64 * 64;
+  if (mode == 2) {   // split the long depth so that every SM has work; each chunk adds its partial tile
+    const int tiles = ((p.rows_a + 127) / 128) * ((p.cols_b + 255) / 256);
+    int chunks = (2 * 148 + tiles - 1) / tiles;
+    const int max_chunks = (p.depth + 1023) / 1024;
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    p.depth_chunk = ((p.depth + chunks - 1) / chunks + 63) / 64 * 64;
+  }
+  p.c = out;
+  p.c_f32 = out_dtype == AR_F32;
+  p.ldc = (int)out_cols;
+  p.accumulate = mode == 2;
+  p.status = st->status;
+  AR_CUDA(launch_linear(ma, mb, p, s), "linear launch");
+  return AR_OK;
+}
+
+AR_API ar_status ar_linear_fwd(void* output, const void* input, const void* weight, int64_t M, int64_t N, int64_t K,
+                               int32_t in_dtype, int32_t out_dtype, void* stream) {
+  return linear_call(0, output, input, weight, M, N, K, in_dtype, out_dtype, stream);
+}
+AR_API ar_status ar_linear_bwd_dx(void* grad_input, const void* grad_output, const void* weight, int64_t M, int64_t N,
+                                  int64_t K, int32_t in_dtype, int32_t out_dtype, void* stream) {
+  return linear_call(1, grad_input, grad_output, weight, M, N, K, in_dtype, out_dtype, stream);
+}
+AR_API ar_status ar_linear_bwd_dw(float* grad_weight, const void* grad_output, const void* input, int64_t M, int64_t N,
+                                  int64_t K, int32_t in_dtype, void* stream) {
+  return linear_call(2, grad_weight, grad_output, input, M, N, K, in_dtype, AR_F32, stream);
+}
+
 // ---- fused family ------------------------------------------------------------------------------
 static ar_status check_params(const ar_attn_params* p) {
   if (!p) return fail(AR_ERR_BAD_ARG, "params is null");

@@ -112,6 +112,20 @@ cudaError_t launch_precompute_d(float* d_out, const T* o, const T* d_o, long lon
 cudaError_t launch_stats_transpose(float* lse2_t, float* dvec_t, const float* lse, const float* dvec,
                                    int B, int T, int H, int t_pad, cudaStream_t stream, RowMap map = RowMap());
 
+// The projection GEMMs (linear.cu): C[rows_a, cols_b] (+)= A B over `depth`, in one of three operand
+// arrangements (mode 0: Y = X W^T, 1: dX = dY W, 2: dW += dY^T X).
+struct LinParams {
+  int mode;
+  int rows_a, cols_b, depth;
+  int depth_chunk;   // depth handled by one work item (a multiple of 64; < depth only for mode 2)
+  void* c;           // output, row-major, leading dimension ldc elements
+  int c_f32;         // element type of c (mode 2: always fp32)
+  int ldc;
+  int accumulate;    // add into c with fp32 reductions instead of storing (mode 2)
+  uint32_t* status;
+};
+cudaError_t launch_linear(const CUtensorMap& map_a, const CUtensorMap& map_b, const LinParams& p, cudaStream_t stream);
+
 // Launches a persistent kernel with programmatic stream serialization allowed (see ptx.cuh).
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream,

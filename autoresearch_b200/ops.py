@@ -74,3 +74,48 @@ def flash_attn_bwd_dkv(grad_k, grad_v, q, k, v, grad_output, lse, d_buf, B, T, n
                                                 _ptr(k, "k"), _ptr(v, "v"), _ptr(grad_output, "grad_output"),
                                                 _ptr(lse, "lse"), _ptr(d_buf, "d_buf"), B, T, num_heads,
                                                 head_dim, window_size, _stream(stream)))
+
+
+def _mat(t: torch.Tensor, name: str, shape, dtypes=(torch.float32, torch.bfloat16)) -> int:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+    if t.dtype not in dtypes:
+        raise ValueError(f"{name} has dtype {t.dtype}")
+    return t.data_ptr()
+
+
+def _dt(t: torch.Tensor) -> int:
+    return _lib.AR_F32 if t.dtype == torch.float32 else _lib.AR_BF16
+
+
+def linear_fwd(output, input, weight, M, N, K, stream=None):
+    """ops.mojo:110-117: output[M,N] = input[M,K] weight[N,K]^T.  input and weight share a dtype
+    (fp32 or bf16); output fp32 or bf16."""
+    if input.dtype != weight.dtype:
+        raise ValueError("input and weight must share a dtype")
+    with torch.cuda.device(input.device):
+        _lib.check(_lib.lib().ar_linear_fwd(_mat(output, "output", (M, N)), _mat(input, "input", (M, K)),
+                                            _mat(weight, "weight", (N, K)), M, N, K, _dt(input), _dt(output),
+                                            _stream(stream)))
+
+
+def linear_bwd_dx(grad_input, grad_output, weight, M, N, K, stream=None):
+    """ops.mojo:870-878: grad_input[M,K] = grad_output[M,N] weight[N,K]."""
+    if grad_output.dtype != weight.dtype:
+        raise ValueError("grad_output and weight must share a dtype")
+    with torch.cuda.device(weight.device):
+        _lib.check(_lib.lib().ar_linear_bwd_dx(_mat(grad_input, "grad_input", (M, K)), _mat(grad_output, "grad_output", (M, N)),
+                                               _mat(weight, "weight", (N, K)), M, N, K, _dt(weight), _dt(grad_input),
+                                               _stream(stream)))
+
+
+def linear_bwd_dw(grad_weight, grad_output, input, M, N, K, stream=None):
+    """ops.mojo:953-961: grad_weight[N,K] += grad_output[M,N]^T input[M,K] (fp32, accumulated)."""
+    if grad_output.dtype != input.dtype:
+        raise ValueError("grad_output and input must share a dtype")
+    with torch.cuda.device(input.device):
+        _lib.check(_lib.lib().ar_linear_bwd_dw(_mat(grad_weight, "grad_weight", (N, K), (torch.float32,)),
+                                               _mat(grad_output, "grad_output", (M, N)), _mat(input, "input", (M, K)),
+                                               M, N, K, _dt(input), _stream(stream)))

@@ -182,6 +182,35 @@ AR_API ar_status ar_flash_attn_bwd_dkv(float* grad_k, float* grad_v, const float
                                        int64_t window_size, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * The projections either side of attention (QKV before it, c_proj after it, and any other linear
+ * layer of the model) on the tensor cores: bf16 operands, fp32 accumulation.  Same argument order
+ * as the reference's matmuls, plus element types: in_dtype (AR_BF16, or AR_F32 = staged as bf16 in
+ * the library's scratch) for both inputs, out_dtype for the result.  All matrices row-major and
+ * contiguous; N and K multiples of 8, the result's row length a multiple of 32; M arbitrary.
+ * What the reference's docstrings state is computed (its kernels write only a quarter of each
+ * output tile, ops.mojo:134-143).
+ * ------------------------------------------------------------------------------------ */
+
+/* replaces linear_fwd (ops.mojo:110-117; launch_linear, model.mojo:162-174):
+ * output[M,N] = input[M,K] weight[N,K]^T. */
+AR_API ar_status ar_linear_fwd(void* output, const void* input, const void* weight, int64_t M,
+                               int64_t N, int64_t K, int32_t in_dtype, int32_t out_dtype,
+                               void* stream);
+
+/* replaces linear_bwd_dx (ops.mojo:870-878; launch_linear_bwd_dx, model.mojo:177-189):
+ * grad_input[M,K] = grad_output[M,N] weight[N,K]. */
+AR_API ar_status ar_linear_bwd_dx(void* grad_input, const void* grad_output, const void* weight,
+                                  int64_t M, int64_t N, int64_t K, int32_t in_dtype,
+                                  int32_t out_dtype, void* stream);
+
+/* replaces linear_bwd_dw (ops.mojo:953-961; launch_linear_bwd_dw, model.mojo:192-204):
+ * grad_weight[N,K] += grad_output[M,N]^T input[M,K]; fp32, ACCUMULATED into grad_weight like the
+ * reference's (zero it first for a plain product).  The sum over M is split over the SMs and
+ * added with fp32 reductions, so its rounding can differ from run to run in the last bits. */
+AR_API ar_status ar_linear_bwd_dw(float* grad_weight, const void* grad_output, const void* input,
+                                  int64_t M, int64_t N, int64_t K, int32_t in_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * (ii) Fused family: one call for the forward launches of model.mojo:668-677 + 694-699
  *      and one for the backward launches of model.mojo:915-935 + 955-964.
  * ------------------------------------------------------------------------------------ */

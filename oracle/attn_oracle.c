@@ -405,3 +405,50 @@ ORACLE_API void oracle_qk_rope_norm(float* q_out, float* k_out, float* rms_q, fl
   oracle_rmsnorm_fwd(q_out, rms_q, q_out, num_tokens * num_heads, head_dim);
   oracle_rmsnorm_fwd(k_out, rms_k, k_out, num_tokens * num_heads, head_dim);
 }
+
+/* ops.mojo:110-117 (linear_fwd): Y[m, n] = sum_k X[m, k] * W[n, k], k ascending, fp32.  This restates
+ * what the kernel's docstring and its accumulation loop state (ops.mojo:118, 170-186); the kernel's
+ * thread-to-output mapping covers only rows / columns 0..3 of every 8 (ops.mojo:134-143, 188-203),
+ * which is not a convention a replacement could follow. */
+ORACLE_API void oracle_linear_fwd(float* y, const float* x, const float* w, int64_t M, int64_t N, int64_t K) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      float acc = 0.0f;
+      for (int64_t k = 0; k < K; ++k) acc += x[m * K + k] * w[n * K + k];
+      y[m * N + n] = acc;
+    }
+}
+
+/* ops.mojo:870-878 (linear_bwd_dx): dX[m, k] = sum_n dY[m, n] * W[n, k], n ascending for every
+ * element (the loops are ordered for locality; each element's own sum order is unchanged). */
+ORACLE_API void oracle_linear_bwd_dx(float* dx, const float* dy, const float* w, int64_t M, int64_t N, int64_t K) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    float* acc = dx + m * K;
+    for (int64_t k = 0; k < K; ++k) acc[k] = 0.0f;
+    for (int64_t n = 0; n < N; ++n) {
+      const float g = dy[m * N + n];
+      for (int64_t k = 0; k < K; ++k) acc[k] += g * w[n * K + k];
+    }
+  }
+}
+
+/* ops.mojo:953-961 (linear_bwd_dw): dW[n, k] += sum_m dY[m, n] * X[m, k], m ascending for every
+ * element, the finished sum added into dW once (ops.mojo:1018-1033). */
+ORACLE_API void oracle_linear_bwd_dw(float* dw, const float* dy, const float* x, int64_t M, int64_t N, int64_t K) {
+#pragma omp parallel
+  {
+    float* acc = (float*)malloc((size_t)K * sizeof(float));
+#pragma omp for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+      for (int64_t k = 0; k < K; ++k) acc[k] = 0.0f;
+      for (int64_t m = 0; m < M; ++m) {
+        const float g = dy[m * N + n];
+        for (int64_t k = 0; k < K; ++k) acc[k] += g * x[m * K + k];
+      }
+      for (int64_t k = 0; k < K; ++k) dw[n * K + k] += acc[k];
+    }
+    free(acc);
+  }
+}

@@ -119,6 +119,33 @@ def qk_rope_norm(q: np.ndarray, k: np.ndarray, cos: np.ndarray, sin: np.ndarray,
     return qo, ko, rq, rk
 
 
+def linear_fwd(x: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """ops.mojo:110-117: Y = X W^T for X [M,K], W [N,K]."""
+    x, w = np.ascontiguousarray(x, np.float32), np.ascontiguousarray(w, np.float32)
+    (M, K), N = x.shape, w.shape[0]
+    y = np.empty((M, N), np.float32)
+    lib().oracle_linear_fwd(_p(y), _p(x), _p(w), _i(M), _i(N), _i(K))
+    return y
+
+
+def linear_bwd_dx(dy: np.ndarray, w: np.ndarray) -> np.ndarray:
+    """ops.mojo:870-878: dX = dY W for dY [M,N], W [N,K]."""
+    dy, w = np.ascontiguousarray(dy, np.float32), np.ascontiguousarray(w, np.float32)
+    (M, N), K = dy.shape, w.shape[1]
+    dx = np.empty((M, K), np.float32)
+    lib().oracle_linear_bwd_dx(_p(dx), _p(dy), _p(w), _i(M), _i(N), _i(K))
+    return dx
+
+
+def linear_bwd_dw(dw: np.ndarray, dy: np.ndarray, x: np.ndarray) -> np.ndarray:
+    """ops.mojo:953-961: dW += dY^T X (returns the updated copy of dw)."""
+    dw = np.array(dw, np.float32, order="C")
+    dy, x = np.ascontiguousarray(dy, np.float32), np.ascontiguousarray(x, np.float32)
+    (M, N), K = dy.shape, x.shape[1]
+    lib().oracle_linear_bwd_dw(_p(dw), _p(dy), _p(x), _i(M), _i(N), _i(K))
+    return dw
+
+
 def flash_attn_fwd(q, k, v, window_size: int):
     """ops.mojo:244-323.  q,k,v [B,T,H,D] fp32 -> (O [B,T,H,D], LSE [B,T,H])."""
     q, k, v = (np.ascontiguousarray(a, np.float32) for a in (q, k, v))
