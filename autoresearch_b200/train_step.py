@@ -229,6 +229,7 @@ class TrainStep:
     reference_quirks: bool = True
     compute_dtype: torch.dtype = torch.bfloat16      # operand type of the matmuls (accumulation is fp32)
     master_dtype: torch.dtype = torch.float32        # residual stream, saved activations, gradients
+    projections: str = "torch"                       # "library": the matmuls through ar_linear_* (bf16 operands)
     grads: Dict[str, torch.Tensor] = field(default_factory=dict)
     process_group: Optional[object] = None
     _pending: List = field(default_factory=list)
@@ -241,6 +242,39 @@ class TrainStep:
     def _mm(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         """a @ b with operands in the compute dtype, result in the master dtype."""
         return (a.to(self.compute_dtype) @ b.to(self.compute_dtype)).to(self.master_dtype)
+
+    def _library(self, *ts: torch.Tensor) -> bool:
+        return self.projections == "library" and all(t.is_cuda and t.dtype in (torch.float32, torch.bfloat16) for t in ts)
+
+    def _lin(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """linear_fwd (ops.mojo:110): x [M, K] times weight [N, K] transposed."""
+        if not self._library(x, weight):
+            return self._mm(x, weight.t())
+        from . import ops
+        (M, K), N = x.shape, weight.shape[0]
+        y = torch.empty(M, N, device=x.device, dtype=self.master_dtype)
+        ops.linear_fwd(y, x.contiguous(), weight.to(x.dtype), M, N, K)
+        return y
+
+    def _lin_dx(self, dy: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """linear_bwd_dx (ops.mojo:870): dy [M, N] times weight [N, K]."""
+        if not self._library(dy, weight):
+            return self._mm(dy, weight)
+        from . import ops
+        (M, N), K = dy.shape, weight.shape[1]
+        dx = torch.empty(M, K, device=dy.device, dtype=self.master_dtype)
+        ops.linear_bwd_dx(dx, dy.contiguous(), weight.to(dy.dtype), M, N, K)
+        return dx
+
+    def _lin_dw(self, name: str, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """linear_bwd_dw (ops.mojo:953): grads[name] [N, K] += dy [M, N] transposed times x [M, K]."""
+        gw = self.grads[name]
+        if not self._library(dy, x) or gw.dtype != torch.float32:
+            gw += self._mm(dy.t(), x)
+            return
+        from . import ops
+        (M, N), K = dy.shape, x.shape[1]
+        ops.linear_bwd_dw(gw, dy.contiguous(), x.to(dy.dtype).contiguous(), M, N, K)
 
     def zero_grads(self):
         for g in self.grads.values():
@@ -294,9 +328,9 @@ class TrainStep:
             L["x"] = x
             xn, L["rms_attn"] = rmsnorm(x, self.master_dtype)
             L["xn"] = xn
-            q = self._mm(xn, w[f"c_q.{i}"].t())
-            k = self._mm(xn, w[f"c_k.{i}"].t())
-            v = self._mm(xn, w[f"c_v.{i}"].t())
+            q = self._lin(xn, w[f"c_q.{i}"])
+            k = self._lin(xn, w[f"c_k.{i}"])
+            v = self._lin(xn, w[f"c_v.{i}"])
             if cfg.has_ve(i):
                 ve = w[f"value_embeds.{i}"][flat]                                               # [BT, kv]
                 gate = 2.0 * torch.sigmoid(xn[:, :VE_GATE_CHANNELS] @ w[f"ve_gate.{i}"].t())    # [BT, H]
@@ -307,20 +341,20 @@ class TrainStep:
                                                  v.view(B, T, H, D).contiguous(), cfg.window_size(i))
             o = o.reshape(-1, C).to(self.master_dtype)
             L["o"] = o
-            x = x + self._mm(o, w[f"c_proj.{i}"].t())
+            x = x + self._lin(o, w[f"c_proj.{i}"])
             L["x_mid"] = x
             xn2, L["rms_mlp"] = rmsnorm(x, self.master_dtype)
             L["xn2"] = xn2
-            hdn = self._mm(xn2, w[f"c_fc.{i}"].t())
+            hdn = self._lin(xn2, w[f"c_fc.{i}"])
             L["h"] = hdn
             act = torch.relu(hdn).pow(2)
             L["act"] = act
-            x = x + self._mm(act, w[f"mlp_proj.{i}"].t())
+            x = x + self._lin(act, w[f"mlp_proj.{i}"])
             sv["layers"].append(L)
         sv["x_pre_final"] = x
         xf, sv["rms_final"] = rmsnorm(x, self.master_dtype)
         sv["x_final"] = xf
-        raw = self._mm(xf, w["lm_head"].t())
+        raw = self._lin(xf, w["lm_head"])
         capped = SOFTCAP * torch.tanh(raw / SOFTCAP)
         sv["raw"], sv["capped"] = raw, capped
         loss = torch.nn.functional.cross_entropy(capped, sv["targets"])
@@ -340,22 +374,22 @@ class TrainStep:
         dlog = probs * (loss_scale / BT)          # w.r.t. the capped logits (mean over tokens, as mean_reduce does)
         if not quirks:
             dlog = dlog * (1.0 - torch.tanh(sv["raw"] / SOFTCAP).pow(2))
-        g["lm_head"] += self._mm(dlog.t(), sv["x_final"])
-        dx = self._mm(dlog, w["lm_head"])
+        self._lin_dw("lm_head", dlog, sv["x_final"])
+        dx = self._lin_dx(dlog, w["lm_head"])
         dx = rmsnorm_bwd(dx, sv["x_pre_final"], sv["rms_final"], self.master_dtype)
         dx0 = torch.zeros_like(dx)
         for i in reversed(range(cfg.n_layer)):
             L = sv["layers"][i]
             # MLP
-            g[f"mlp_proj.{i}"] += self._mm(dx.t(), L["act"])
-            dact = self._mm(dx, w[f"mlp_proj.{i}"])
+            self._lin_dw(f"mlp_proj.{i}", dx, L["act"])
+            dact = self._lin_dx(dx, w[f"mlp_proj.{i}"])
             dh = 2.0 * L["h"] * dact * (L["h"] > 0)
-            g[f"c_fc.{i}"] += self._mm(dh.t(), L["xn2"])
-            dxn2 = self._mm(dh, w[f"c_fc.{i}"])
+            self._lin_dw(f"c_fc.{i}", dh, L["xn2"])
+            dxn2 = self._lin_dx(dh, w[f"c_fc.{i}"])
             dx = dx + rmsnorm_bwd(dxn2, L["x"] if quirks else L["x_mid"], L["rms_mlp"], self.master_dtype)
             # attention
-            g[f"c_proj.{i}"] += self._mm(dx.t(), L["o"])
-            d_o = self._mm(dx, w[f"c_proj.{i}"])
+            self._lin_dw(f"c_proj.{i}", dx, L["o"])
+            d_o = self._lin_dx(dx, w[f"c_proj.{i}"])
             dq, dk, dv = self.attention.backward(L["ctx"], d_o.view(B, T, H, D))
             dq, dk, dv = (t.reshape(BT, H * D).to(self.master_dtype) for t in (dq, dk, dv))
             if not quirks:
@@ -372,10 +406,10 @@ class TrainStep:
                 dve = (L["gate"].unsqueeze(-1) * dvh).reshape(BT, H * D)
                 dgate = (L["ve"].view(BT, H, D) * dvh).sum(-1)                                   # [BT, H]
                 g[f"value_embeds.{i}"].index_add_(0, ids, dve)
-            g[f"c_q.{i}"] += self._mm(dq.t(), xn)
-            g[f"c_k.{i}"] += self._mm(dk.t(), xn)
-            g[f"c_v.{i}"] += self._mm(dv.t(), xn)
-            dxn = self._mm(dq, w[f"c_q.{i}"]) + self._mm(dk, w[f"c_k.{i}"]) + self._mm(dv, w[f"c_v.{i}"])
+            self._lin_dw(f"c_q.{i}", dq, xn)
+            self._lin_dw(f"c_k.{i}", dk, xn)
+            self._lin_dw(f"c_v.{i}", dv, xn)
+            dxn = self._lin_dx(dq, w[f"c_q.{i}"]) + self._lin_dx(dk, w[f"c_k.{i}"]) + self._lin_dx(dv, w[f"c_v.{i}"])
             if cfg.has_ve(i):
                 dz = dgate * L["gate"] * (1.0 - L["gate"] / 2.0)
                 g[f"ve_gate.{i}"] += dz.t() @ xn[:, :VE_GATE_CHANNELS]

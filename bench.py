@@ -409,6 +409,38 @@ def run_gpu(args):
         hbm_kernel("precompute_d128<f32>", lambda: ab.flash_attn_bwd_precompute_d(dsc, f32[1], f32[2], B, T, H, D),
                    n_el * 8 + B * T * H * 4, "ar_flash_attn_bwd_precompute_d on fp32 O, dO")
         del f32, b16, dsc
+        # the projections either side of the path (linear_fwd / _bwd_dx / _bwd_dw, ops.mojo:110, 870, 953) at
+        # this config's token count: one head group's projection (N = K = H*D) as the reference launches
+        # it, and q, k, v as one N = 3*H*D product; bf16 in and out, operand sets cycled so that no
+        # launch finds its operands in L2
+        Mtok, C = B * T, H * D
+
+        def gemm_kernel(name, call, N, K, what):
+            sets = max(2, int(192e6 / (2.0 * Mtok * (N + K))) + 1)
+            xs = [torch.randn(Mtok, K, device=dev, generator=gen).bfloat16() for _ in range(sets)]
+            dys = [torch.randn(Mtok, N, device=dev, generator=gen).bfloat16() for _ in range(sets)]
+            wt = (torch.randn(N, K, device=dev, generator=gen) * 0.05).bfloat16()
+            dws = torch.zeros(N, K, device=dev)
+            it = [0]
+
+            def fn():
+                i = it[0] % sets
+                it[0] += 1
+                call(xs[i], dys[i], wt, dws, Mtok, N, K)
+            fn()
+            ms = timed(lambda: [fn() for _ in range(sets)], 5) / (5 * sets)
+            fl = 2.0 * Mtok * N * K
+            kernels[name] = {"bound": "tensor", "ms_per_launch": round(ms, 4), "achieved": fl / (ms * 1e-3) / 1e12,
+                             "unit": "TFLOP/s", "frac": fl / (ms * 1e-3) / 1e12 / peak, "peak": peak,
+                             "M": Mtok, "N": N, "K": K, "what": what}
+
+        for tag, N in (("", C), ("_qkv", 3 * C)):
+            gemm_kernel("linear_fwd" + tag, lambda x, dy, w_, dw, M, N, K: ab.linear_fwd(dy, x, w_, M, N, K), N, C,
+                        "ar_linear_fwd, bf16 in and out")
+            gemm_kernel("linear_bwd_dx" + tag, lambda x, dy, w_, dw, M, N, K: ab.linear_bwd_dx(x, dy, w_, M, N, K), N, C,
+                        "ar_linear_bwd_dx, bf16 in and out")
+            gemm_kernel("linear_bwd_dw" + tag, lambda x, dy, w_, dw, M, N, K: ab.linear_bwd_dw(dw, dy, x, M, N, K), N, C,
+                        "ar_linear_bwd_dw, bf16 in, fp32 accumulated")
         dominant = max(per_pair, key=lambda n: phase[n])
         kd = kernels[dominant]
         roofline = {"bound": "tensor", "kernel": dominant, "achieved": kd["achieved"], "peak": peak, "unit": "TFLOP/s",
@@ -618,7 +650,8 @@ def run_config3(args):
     B, T = args.batch or 16, cfg.sequence_len
     weights = ts.init_weights(cfg, dev, test_init=True)     # non-zero c_proj / mlp_proj (test_forward.mojo:48-63)
     attn = ts.LibraryAttention(cfg, T, dev)
-    step = ts.TrainStep(cfg, weights, attn, reference_quirks=True, process_group=True if world > 1 else None)
+    step = ts.TrainStep(cfg, weights, attn, reference_quirks=True, process_group=True if world > 1 else None,
+                        projections=args.projections)
     gen = torch.Generator(device=dev).manual_seed(7 + rank)
     ids = torch.randint(0, cfg.vocab_size, (B, T), device=dev, generator=gen)
     targets = torch.cat([ids[:, 1:], torch.randint(0, cfg.vocab_size, (B, 1), device=dev, generator=gen)], dim=1)
@@ -655,10 +688,11 @@ def run_config3(args):
         "metric": "gpt_train_step_tokens_per_s", "value": world * B * T / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "BASELINE config 3 per GPU: small-GPT forward + backward, attention on libarattn.so, other "
-                               "layers torch (cuBLAS bf16 matmuls, fp32 residual stream)", "B_per_gpu": B, "T": T,
+        "config": {"workload": "BASELINE config 3 per GPU: small-GPT forward + backward, attention on libarattn.so, the "
+                               "other layers torch operations on an fp32 residual stream", "B_per_gpu": B, "T": T,
                    "n_layer": cfg.n_layer, "n_embd": cfg.n_embd, "n_head": cfg.n_head, "vocab": cfg.vocab_size,
                    "windows": windows, "parameters": n_param, "backward": "as the reference computes it",
+                   "projections": "ar_linear_* (libarattn.so)" if args.projections == "library" else "torch matmul",
                    "parallelism": f"data parallel over {world} rank(s), per-layer gradient buckets all-reduced with NCCL"},
         "loss": float(loss),
         "attention": {"ms_per_step": attn_ms, "share_of_step": attn_ms / ms,
@@ -682,6 +716,8 @@ def main():
                     help="saved: forward rotates Q/K once into saved buffers that backward reuses; "
                          "fused: forward rotates on load, backward rotates in a pre-pass; "
                          "prepass: both passes rotate in a pre-pass")
+    ap.add_argument("--projections", default="library", choices=["library", "torch"],
+                    help="config 3: the model's matmuls through ar_linear_* or through torch")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-phases", action="store_true", help="skip the per-kernel timing behind `roofline`")

@@ -1,4 +1,5 @@
-"""GPU test of the train-step harness with the library's attention back end: on a small model the
+"""GPU test of the train-step harness with the library's attention back end (and, with
+projections="library", the library's projection GEMMs in place of torch's): on a small model the
 loss and the gradients agree with the same step run on the CPU in fp64 with the plain-torch attention
 stand-in, to the accuracy bf16 matmul operands allow."""
 import pytest
@@ -11,8 +12,9 @@ from tests.torch_attention import TorchAttention
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("projections", ["torch", "library"])
 @pytest.mark.parametrize("quirks", [True, False])
-def test_step_matches_cpu_fp64(cuda_device, quirks):
+def test_step_matches_cpu_fp64(cuda_device, quirks, projections):
     cfg = ab.GPTConfig(sequence_len=384, vocab_size=512, n_layer=4, n_head=2, n_kv_head=2, n_embd=256, head_dim=128)
     B, T = 2, cfg.sequence_len
     torch.manual_seed(3)
@@ -33,7 +35,8 @@ def test_step_matches_cpu_fp64(cuda_device, quirks):
                        compute_dtype=torch.float64, master_dtype=torch.float64)
     loss_ref = ref.step(ids, targets)
     wd = {k: v.cuda() for k, v in w.items()}
-    dev = ts.TrainStep(cfg, wd, ts.LibraryAttention(cfg, T, "cuda"), reference_quirks=quirks)
+    dev = ts.TrainStep(cfg, wd, ts.LibraryAttention(cfg, T, "cuda"), reference_quirks=quirks,
+                       projections=projections)
     loss_dev = dev.step(ids.cuda(), targets.cuda())
     ab.check_device_status()
     assert abs(float(loss_dev) - float(loss_ref)) < 2e-3 * float(loss_ref)
