@@ -528,6 +528,10 @@ static ar_status linear_call(int mode, void* out, const void* a_in, const void* 
   if (out_dtype != AR_F32 && out_dtype != AR_BF16) return fail(AR_ERR_UNSUPPORTED, "out_dtype %d unknown", out_dtype);
   if (mode == 2 && out_dtype != AR_F32) return fail(AR_ERR_UNSUPPORTED, "dw is accumulated in fp32");
   if (!aligned16(out) || !aligned16(a_in) || !aligned16(b_in)) return fail(AR_ERR_BAD_ARG, "pointers must be 16-byte aligned");
+  // fp32 operands are staged as bf16 copies before the product starts, so the output may be one of
+  // them (the reference's in-place c_proj backward, model.mojo:906); bf16 operands are read in place
+  if (in_dtype == AR_BF16 && (out == a_in || out == b_in))
+    return fail(AR_ERR_BAD_ARG, "the output aliases a bf16 operand");
   DeviceState* st;
   AR_TRY(device_state(&st));
   cudaStream_t s = (cudaStream_t)stream;

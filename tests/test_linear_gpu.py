@@ -133,3 +133,19 @@ def test_linear_rejects_what_it_cannot_tile(cuda_device):
         ab.linear_fwd(torch.zeros(64, 32, device="cuda"), x, w, 64, 32, 60)   # K not a multiple of 8
     with pytest.raises(ValueError):
         ab.linear_fwd(torch.zeros(64, 32, device="cuda"), x.float(), w, 64, 32, 60)
+
+
+def test_linear_bwd_dx_in_place_on_fp32(cuda_device):
+    """The reference calls linear_bwd_dx with grad_input = grad_output (model.mojo:906, square c_proj):
+    with fp32 operands the call stages them first, so the in-place form gives the same result."""
+    import torch
+    M = N = K = 512
+    rng = np.random.default_rng(21)
+    dy, w = _rand(rng, (M, N)), _rand(rng, (N, K), scale=0.1)
+    buf, wd = _dev(dy, torch.float32), _dev(w, torch.float32)
+    ab.linear_bwd_dx(buf, buf, wd, M, N, K)
+    torch.cuda.synchronize()
+    assert (np.abs(buf.cpu().numpy() - orc.linear_bwd_dx(dy, w)) <= _bound(np.abs(dy) @ np.abs(w))).all()
+    b16 = _dev(dy, torch.bfloat16)
+    with pytest.raises(ab.ArattnError):
+        ab.linear_bwd_dx(b16, b16, _dev(w, torch.bfloat16), M, N, K)
