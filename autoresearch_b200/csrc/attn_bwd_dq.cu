@@ -28,10 +28,10 @@
 // D = rowsum(O * dO) for the queries of the item after the one in flight, replacing
 // flash_attn_bwd_precompute_d (ops.mojo:329-346) and the key-stationary re-layout the dK/dV
 // kernel needs.
-// At the end of an item warpgroups 0 and 1 pull the dQ rows into registers (which frees the
-// accumulator for the next item), multiply by 1/sqrt(D) (ops.mojo:411), apply the inverse rotation
-// of rope_bwd when asked, and write the rows out with plain coalesced stores through per-warp
-// transposition buffers.  Those live in the V-ring slot that held the item's last V tile: the next
+// At the end of an item the four warpgroups pull the dQ rows into registers, a quarter of the columns
+// each (which frees the accumulator for the next item), multiply by 1/sqrt(D) (ops.mojo:411), apply
+// the inverse rotation of rope_bwd when asked, and write the rows out with plain coalesced stores
+// through per-warp transposition buffers.  Those live in the V-ring slot that held the item's last V tile: the next
 // item needs that slot only for its second V tile, and the TMA warp holds that one load back until
 // the write-out is done.
 #include <type_traits>
@@ -54,7 +54,7 @@ struct DqSmem {
   alignas(1024) uint8_t v[kDqVStages][kTileBytes];
   alignas(8) uint64_t x_full, x_free;
   uint64_t k_full[kDqKStages], k_empty[kDqKStages], v_full[kDqVStages], v_empty[kDqVStages];
-  uint64_t g_full, g_free, ready, ds_free, acc_done, acc_free, epi_free, d_ready[2], d_taken[2];   // per D buffer (even / odd items)
+  uint64_t g_full, g_free, ready[2], ds_free[2], acc_done, acc_free, epi_free, d_ready[2], d_taken[2];   // ready, ds_free: per dS buffer (even / odd tiles); d_*: per D buffer (even / odd items)
   alignas(16) float d_row[2][kTile];   // D of the item's 128 queries when this kernel computes it (even / odd items)
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -109,11 +109,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // per-tile barriers: every compute thread arrives (measured 2 % faster for the whole kernel
     // than one elected lane per warp behind a __syncwarp)
     mbar_init(smem_u32(&sm.g_free), kDqCW * 32);  // every compute thread has its columns in registers
-    mbar_init(smem_u32(&sm.ready), kDqCW * 32);   // dS written
-    mbar_init(smem_u32(&sm.ds_free), 1);     // dQ MMAs of the tile have consumed dS
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm.ready[i]), kDqCW * 32);   // dS of a tile written into buffer i
+      mbar_init(smem_u32(&sm.ds_free[i]), 1);          // the dQ MMAs of that tile have consumed it
+    }
     mbar_init(smem_u32(&sm.acc_done), 1);
-    mbar_init(smem_u32(&sm.acc_free), 8);    // the eight write-out warps hold their dQ rows
-    mbar_init(smem_u32(&sm.epi_free), 8);    // ... and have read their transposition buffers
+    mbar_init(smem_u32(&sm.acc_free), kDqCW);    // every compute warp holds its share of the dQ rows
+    mbar_init(smem_u32(&sm.epi_free), kDqCW);    // ... and has read its transposition buffer
     sm.abort_flag = 0u;
     fence_mbar_init();
     prefetch_tmap(&map_q);
@@ -137,7 +139,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   __syncthreads();
   const bool live = ld_shared_u32(smem_u32(&sm.abort_flag)) == 0u;
   const uint32_t tmem = sm.tmem_base;
-  constexpr uint32_t kColDQ = 0, kColS = 128, kColDP = 256, kColDS = 384, kColDSLo = 448;
+  // dS of tile g goes to buffer g & 1 (64 columns each), so that the element-wise stage of a tile does
+  // not wait for the dQ products of the tile before it; a two-term tile puts its residual into the
+  // other buffer and so needs both.
+  constexpr uint32_t kColDQ = 0, kColS = 128, kColDP = 256, kColDS = 384;
   // Tile kb .. kb+127 against the queries row0 .. row0+127: can it hold the keys of a query that sees
   // fewer than 16 keys in all?  Those are the first 15 queries of a sequence (their keys lie in the
   // first tile) and, under a window below 15, every query (its keys lie in the tiles a mask edge
@@ -250,23 +255,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const DqItem wi = dq_item(item, p.dims, n_qt);
       for (int it = 0; it < wi.n_it; ++it, ++g) {
         const int s = g % kDqKStages;
+        const uint32_t bsel = g & 1;
         // ready follows g_full, which follows k_full: K of this stage is in place
-        if (!mbar_wait(w, smem_u32(&sm.ready), g & 1)) { ok = false; break; }
+        if (!mbar_wait(w, smem_u32(&sm.ready[bsel]), (g >> 1) & 1)) { ok = false; break; }
         // the item's first product overwrites dQ: the previous item's rows must have left
         if (it == 0 && n > 0 && !mbar_wait(w, smem_u32(&sm.acc_free), (n - 1) & 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t ka = smem_u32(sm.k[s]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts_elect(tmem + kColDQ, tmem + kColDS + ks * 8, make_sdesc_sw128(ka + ks * 2048, kHalfBytes, 1024),
+          umma_ts_elect(tmem + kColDQ, tmem + kColDS + 64 * bsel + ks * 8, make_sdesc_sw128(ka + ks * 2048, kHalfBytes, 1024),
                         idesc, (it > 0 || ks > 0) ? 1u : 0u);
         if (two_term_tile((wi.jlo + it) * kTile, wi.row0)) {   // the residual term of dS
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
-            umma_ts_elect(tmem + kColDQ, tmem + kColDSLo + ks * 8, make_sdesc_sw128(ka + ks * 2048, kHalfBytes, 1024),
-                          idesc, 1u);
+            umma_ts_elect(tmem + kColDQ, tmem + kColDS + 64 * (bsel ^ 1u) + ks * 8,
+                          make_sdesc_sw128(ka + ks * 2048, kHalfBytes, 1024), idesc, 1u);
         }
-        umma_commit_elect(smem_u32(&sm.ds_free));
+        umma_commit_elect(smem_u32(&sm.ds_free[bsel]));
         umma_commit_elect(smem_u32(&sm.k_empty[s]));
       }
       if (!ok) break;
@@ -354,6 +360,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const f32x2 sc2 = f2_pack(p.scale_log2e, p.scale_log2e);
     int g = 0, n = 0;
     bool ok = true;
+    bool prev_two = false;   // the tile before this one (of this or the previous item) used both dS buffers
     const bool fuse_d = p.o_for_d != nullptr;
     for (int k = 0; ok; ++k) {
       const int item = sched_item(k, n_items);
@@ -429,54 +436,54 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (kMayTwo)   // the rounding residual dS - bf16(dS), exact in fp32
             pl[i] = pack_bf16x2_alu(s0 - bf16_lo_to_f32(pd[i]), s1 - bf16_hi_to_f32(pd[i]));
         }
-        // the dQ MMAs of the previous tile must have consumed the dS region
-        if (g > 0 && !mbar_wait(w, smem_u32(&sm.ds_free), (g - 1) & 1)) { ok = false; break; }
-        tmem_st16(tmem + lane_off + kColDS + wg * 16, pd);
-        if (kMayTwo && two_terms) tmem_st16(tmem + lane_off + kColDSLo + wg * 16, pl);
+        // Buffer g & 1 was last read by the dQ MMAs of tile g - 2.  The other buffer belongs to tile
+        // g - 1: its MMAs must be done as well if that tile also kept its residual in this buffer, or if
+        // this tile is about to put its own residual there.  (One barrier per buffer: a waiter on a
+        // single barrier would fall two phases behind, which a parity wait cannot express.)
+        const uint32_t bsel = g & 1;
+        if (g > 1 && !mbar_wait(w, smem_u32(&sm.ds_free[bsel]), ((g >> 1) - 1) & 1)) { ok = false; break; }
+        if (g > 0 && (prev_two || two_terms) &&
+            !mbar_wait(w, smem_u32(&sm.ds_free[bsel ^ 1u]), ((g - 1) >> 1) & 1)) { ok = false; break; }
+        tmem_st16(tmem + lane_off + kColDS + 64 * bsel + wg * 16, pd);
+        if (kMayTwo && two_terms) tmem_st16(tmem + lane_off + kColDS + 64 * (bsel ^ 1u) + wg * 16, pl);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(smem_u32(&sm.ready));
+        mbar_arrive(smem_u32(&sm.ready[bsel]));
+        prev_two = two_terms;
       }
       };
       if (row0 == 0 || (window > 0 && window < 15)) tile_loop(std::true_type{});
       else tile_loop(std::false_type{});
       if (!ok) break;
-      if (wg < 2) {
+      {
+        // Write-out by all four warpgroups: warpgroup c takes the column pairs (d, d + 64) with d in
+        // [16c, 16c + 16) of its rows.  The table values of the inverse rotation are fetched (in the
+        // layout the rows have after their transposition, see warp_store_pair16) before the wait for
+        // the item's last products.
+        const bool rot = p.cos_buf != nullptr;
+        const int wrow0 = row0 + 32 * (warp & 3);
+        RotTable rt;
+        if (rot) rot_table_fetch(rt, p.cos_buf, p.sin_buf, wrow0, lane, wg * 16, T);
         if (!mbar_wait(w, smem_u32(&sm.acc_done), n & 1)) { ok = false; break; }
         tc_fence_after();
-        // warpgroup c holds the (d, d+64) column-chunk pair c of its rows
-        uint32_t a[32], bq[32];
-        tmem_ld32x2_wait(tmem + lane_off + kColDQ + wg * 32, a, tmem + lane_off + kColDQ + 64 + wg * 32, bq);
+        uint32_t a[16], bq[16];
+        tmem_ld16x2_wait(tmem + lane_off + kColDQ + wg * 16, a, tmem + lane_off + kColDQ + 64 + wg * 16, bq);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm.acc_free));
-        float lo_v[32], hi_v[32];
+        float lo_v[16], hi_v[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 16; ++i) {
           lo_v[i] = __uint_as_float(a[i]) * (p.scale * kTruncGainInv);   // dS carried the gain of P'
           hi_v[i] = __uint_as_float(bq[i]) * (p.scale * kTruncGainInv);
-        }
-        if (p.cos_buf != nullptr) {
-          const int pos = min(row, T - 1);
-          const float4* cp = reinterpret_cast<const float4*>(p.cos_buf + (size_t)pos * 64 + wg * 32);
-          const float4* sp = reinterpret_cast<const float4*>(p.sin_buf + (size_t)pos * 64 + wg * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
-            rope_bwd_pair(lo_v[4 * i], hi_v[4 * i], cv.x, sv.x);
-            rope_bwd_pair(lo_v[4 * i + 1], hi_v[4 * i + 1], cv.y, sv.y);
-            rope_bwd_pair(lo_v[4 * i + 2], hi_v[4 * i + 2], cv.z, sv.z);
-            rope_bwd_pair(lo_v[4 * i + 3], hi_v[4 * i + 3], cv.w, sv.w);
-          }
         }
         // transposition buffer of this warp: 2 KB of the V slot that held the item's last V tile
         const uint32_t epi = smem_u32(sm.v[(g - 1) % kDqVStages]) + warp * 2048u;
         const int esize = p.grad_f32 ? 4 : 2;
-        const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
-        const int wrow0 = row0 + 32 * (warp & 3);
         uint8_t* gout = static_cast<uint8_t*>(p.dq) + row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
-        warp_store_32cols(epi, lane, lo_v, gout + (size_t)(wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
-        warp_store_32cols(epi, lane, hi_v, gout + (size_t)(64 + wg * 32) * esize, row_stride, T - wrow0, p.grad_f32);
+        const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
+        if (rot) warp_store_pair16<true>(epi, lane, lo_v, hi_v, rt, gout, row_stride, wg * 16, T - wrow0, p.grad_f32);
+        else warp_store_pair16<false>(epi, lane, lo_v, hi_v, rt, gout, row_stride, wg * 16, T - wrow0, p.grad_f32);
         fence_proxy_async_smem();   // the slot is next written by a bulk tensor load
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm.epi_free));

@@ -282,6 +282,53 @@ __device__ __forceinline__ void warp_store_32cols(uint32_t epi, int lane, const 
   }
 }
 
+// Same for 16 consecutive values per lane: rows of 64 bytes (fp32, eight rows per store instruction)
+// or 32 bytes (bf16, sixteen rows per instruction) through at most 2 KB of the warp's buffer.
+__device__ __forceinline__ void warp_store_16cols(uint32_t epi, int lane, const float (&v)[16], uint8_t* grow0,
+                                                  size_t row_stride_bytes, int rows_valid, int out_f32) {
+  if (out_f32) {
+    const uint32_t wsw = (lane >> 1) & 3u;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j)
+      sts128(epi + lane * 64u + ((j ^ wsw) << 4),
+             make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
+                        __float_as_uint(v[4 * j + 3])));
+    __syncwarp();
+    uint4 t[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t row = 8 * k + (lane >> 2), j = lane & 3;
+      t[k] = lds128(epi + row * 64u + ((j ^ ((row >> 1) & 3u)) << 4));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = 8 * k + (lane >> 2), j = lane & 3;
+      if (row < rows_valid) *reinterpret_cast<uint4*>(grow0 + (size_t)row * row_stride_bytes + j * 16) = t[k];
+    }
+    __syncwarp();
+  } else {
+    const uint32_t wsw = (lane >> 2) & 1u;
+#pragma unroll
+    for (uint32_t j = 0; j < 2; ++j)
+      sts128(epi + lane * 32u + ((j ^ wsw) << 4),
+             make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                        pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7])));
+    __syncwarp();
+    uint4 t[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t row = 16 * k + (lane >> 1), j = lane & 1;
+      t[k] = lds128(epi + row * 32u + ((j ^ ((row >> 2) & 1u)) << 4));
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int row = 16 * k + (lane >> 1), j = lane & 1;
+      if (row < rows_valid) *reinterpret_cast<uint4*>(grow0 + (size_t)row * row_stride_bytes + j * 16) = t[k];
+    }
+    __syncwarp();
+  }
+}
+
 // In-register inverse rotation of a full fp32 row (rope_bwd, ops.mojo:1119-1120):
 //   dx1 = dy1*c - dy2*s ; dx2 = dy1*s + dy2*c
 __device__ __forceinline__ void rope_bwd_pair(float& g1, float& g2, float c, float s) {
@@ -290,6 +337,80 @@ __device__ __forceinline__ void rope_bwd_pair(float& g1, float& g2, float c, flo
   g1 = a;
   g2 = b;
 }
+
+// Write-out of the column pairs (d, d + 64), d in [col0, col0 + 16), of a warp's 32 rows (lane = row)
+// with the inverse rotation of rope_bwd (ops.mojo:1119-1120) applied AFTER the transposition, where a
+// lane holds four consecutive columns of one row: the cos / sin values it needs are then 16 bytes that
+// eight rows' worth of lanes fetch as whole 64-byte segments (`cs`, `sn`: fetched by the caller with
+// rot_table_fetch, early, so that their latency is hidden), instead of every lane gathering its own
+// row of the table (32 lines per instruction, several thousand cycles per item).  The rows leave 16
+// at a time through 2 KB of the warp's buffer (1 KB per half of the pair); fp32 rows as 64-byte
+// segments, bf16 rows as 32-byte segments.
+struct RotTable {
+  float4 c[2][2], s[2][2];   // [16-row half][8-row group]
+};
+__device__ __forceinline__ void rot_table_fetch(RotTable& t, const float* cos_buf, const float* sin_buf, int row0_warp,
+                                                int lane, int col0, int T) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int pos = min(row0_warp + 16 * h + 8 * k + (lane >> 2), T - 1);
+      const size_t off = (size_t)pos * 64 + col0 + 4 * (lane & 3);
+      t.c[h][k] = __ldg(reinterpret_cast<const float4*>(cos_buf + off));
+      t.s[h][k] = __ldg(reinterpret_cast<const float4*>(sin_buf + off));
+    }
+}
+template <bool kRot>
+__device__ __forceinline__ void warp_store_pair16(uint32_t epi, int lane, const float (&lo)[16], const float (&hi)[16],
+                                                  const RotTable& rot, uint8_t* grow0, size_t row_stride_bytes,
+                                                  int col0, int rows_valid, int out_f32) {
+  const int esize = out_f32 ? 4 : 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if ((lane >> 4) == h) {
+      const uint32_t rl = lane & 15, wsw = (rl >> 1) & 3u;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        sts128(epi + rl * 64u + ((j ^ wsw) << 4),
+               make_uint4(__float_as_uint(lo[4 * j]), __float_as_uint(lo[4 * j + 1]), __float_as_uint(lo[4 * j + 2]),
+                          __float_as_uint(lo[4 * j + 3])));
+        sts128(epi + 1024u + rl * 64u + ((j ^ wsw) << 4),
+               make_uint4(__float_as_uint(hi[4 * j]), __float_as_uint(hi[4 * j + 1]), __float_as_uint(hi[4 * j + 2]),
+                          __float_as_uint(hi[4 * j + 3])));
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t rl = 8 * k + (lane >> 2), j = lane & 3;
+      const uint32_t off = rl * 64u + ((j ^ ((rl >> 1) & 3u)) << 4);
+      const uint4 a = lds128(epi + off), b = lds128(epi + 1024u + off);
+      float x[4] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w)};
+      float y[4] = {__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w)};
+      if (kRot) {
+        const float4 c = rot.c[h][k], s = rot.s[h][k];
+        rope_bwd_pair(x[0], y[0], c.x, s.x);
+        rope_bwd_pair(x[1], y[1], c.y, s.y);
+        rope_bwd_pair(x[2], y[2], c.z, s.z);
+        rope_bwd_pair(x[3], y[3], c.w, s.w);
+      }
+      const int row = 16 * h + (int)rl;
+      if (row < rows_valid) {
+        uint8_t* g = grow0 + (size_t)row * row_stride_bytes + (size_t)(col0 + 4 * j) * esize;
+        if (out_f32) {
+          *reinterpret_cast<float4*>(g) = make_float4(x[0], x[1], x[2], x[3]);
+          *reinterpret_cast<float4*>(g + 64 * 4) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+          *reinterpret_cast<uint2*>(g) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+          *reinterpret_cast<uint2*>(g + 64 * 2) = make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
 
 // Write-out of two 32-column blocks A and B of an fp32 accumulator in tensor memory (this warp's
 // 32 lanes = 32 consecutive rows; block B lies 64 columns after A, i.e. the two hold the column

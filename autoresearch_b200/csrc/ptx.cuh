@@ -371,6 +371,18 @@ __device__ __forceinline__ void tmem_ld32x2_wait(uint32_t taddr_a, uint32_t (&a)
       : "r"(taddr_a), "r"(taddr_b)
       : "memory");
 }
+// Two 16-column loads in flight, one wait.
+__device__ __forceinline__ void tmem_ld16x2_wait(uint32_t taddr_a, uint32_t (&a)[16], uint32_t taddr_b,
+                                                 uint32_t (&b)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%32];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%33];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]),
+        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15])
+      : "r"(taddr_a), "r"(taddr_b)
+      : "memory");
+}
 // A whole 128-column fp32 row (four 32-column loads in flight, one wait).
 __device__ __forceinline__ void tmem_ld128_wait(uint32_t taddr, uint32_t (&r)[128]) {
   asm volatile(

@@ -247,13 +247,14 @@ def run_dkv(B,H,T,W,c,G=148):
 def dq_item(item,B,H,T,W,n_qt):
     bh=B*H; qi=item//bh; row0=(n_qt-1-qi)*128
     klo=max(0,row0-W) if W>0 else 0; khi=min(row0+127,T-1)
-    return dict(n_it=(khi>>7)-(klo>>7)+1)
+    return dict(n_it=(khi>>7)-(klo>>7)+1, jlo=klo>>7, row0=row0)
 def run_dq(B,H,T,W,c,fuse,G=148):
     n_qt=(T+127)//128; n_items=n_qt*B*H
     bars={}
     def mk(n,cnt): bars[n]=Bar(n,cnt)
-    mk('x_full',1); mk('x_free',2); mk('g_full',2); mk('g_free',4); mk('ready',4); mk('ds_free',1)
-    mk('acc_done',1); mk('acc_free',2); mk('epi_free',2)
+    mk('x_full',1); mk('x_free',2); mk('g_full',2); mk('g_free',4)
+    for i in range(2): mk(f'ready{i}',4); mk(f'ds_free{i}',1)
+    mk('acc_done',1); mk('acc_free',4); mk('epi_free',4)
     for s in range(3): mk(f'k_full{s}',1); mk(f'k_empty{s}',2)
     for s in range(2): mk(f'v_full{s}',1); mk(f'v_empty{s}',1); mk(f'd_ready{s}',1); mk(f'd_taken{s}',4)
     def tma():
@@ -291,9 +292,9 @@ def run_dq(B,H,T,W,c,fuse,G=148):
             wi=dq_item(item,B,H,T,W,n_qt)
             for it in range(wi['n_it']):
                 s=g%3
-                yield ('wait','ready',g&1)
+                yield ('wait',f'ready{g&1}',(g>>1)&1)
                 if it==0 and n>0: yield ('wait','acc_free',(n-1)&1)
-                yield ('arrive','ds_free',1); yield ('arrive',f'k_empty{s}',1)
+                yield ('arrive',f'ds_free{g&1}',1); yield ('arrive',f'k_empty{s}',1)
                 g+=1
             yield ('arrive','acc_done',1); n+=1
     def dwarps():
@@ -301,8 +302,13 @@ def run_dq(B,H,T,W,c,fuse,G=148):
         for item in items_of(c,G,n_items):
             if n>1: yield ('wait',f'd_taken{n&1}',((n>>1)-1)&1)
             yield ('arrive',f'd_ready{n&1}',1); n+=1
+    def two_term(wi,it):
+        # tiles that can hold queries with fewer than 16 visible keys keep a residual in the other dS buffer
+        kb=(wi['jlo']+it)*128; row0=wi['row0']
+        if 0<W<15: return kb+127>row0 or kb<row0+127-W
+        return row0==0 and kb==0
     def compute(wg):
-        g=0;n=0
+        g=0;n=0;prev_two=False
         for item in items_of(c,G,n_items):
             wi=dq_item(item,B,H,T,W,n_qt)
             for it in range(wi['n_it']):
@@ -310,11 +316,13 @@ def run_dq(B,H,T,W,c,fuse,G=148):
                 yield ('arrive','g_free',1)
                 if it==0 and fuse:
                     yield ('wait',f'd_ready{n&1}',(n>>1)&1); yield ('arrive',f'd_taken{n&1}',1)
-                if g>0: yield ('wait','ds_free',(g-1)&1)
-                yield ('arrive','ready',1)
+                two=two_term(wi,it)
+                if g>1: yield ('wait',f'ds_free{g&1}',((g>>1)-1)&1)
+                if g>0 and (prev_two or two): yield ('wait',f'ds_free{(g-1)&1}',((g-1)>>1)&1)
+                yield ('arrive',f'ready{g&1}',1)
+                prev_two=two
                 g+=1
-            if wg<2:
-                yield ('wait','acc_done',n&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
+            yield ('wait','acc_done',n&1); yield ('arrive','acc_free',1); yield ('arrive','epi_free',1)
             n+=1
     ag={'tma':tma(),'isS':issuer(0),'isP':issuer(1),'isQ':dqiss()}
     for wg in range(4): ag[f'wg{wg}']=compute(wg)

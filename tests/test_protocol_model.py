@@ -6,9 +6,10 @@ import pytest
 import protocol_model as pm
 
 # B, H, T, W: ragged ends with one valid row and several rounds of items, one item per CTA, the
-# benchmark shapes, a window of one key, more items than three rounds
+# benchmark shapes, a window of one key, more items than three rounds, a window under 15 keys over
+# several tiles (every edge tile keeps a dS residual in the second buffer)
 SHAPES = [(12, 3, 2049, 1000), (19, 5, 2049, 100), (10, 4, 1100, 300), (7, 6, 1100, 0), (16, 4, 2048, 1024),
-          (16, 4, 2048, 0), (3, 5, 333, 77), (40, 4, 129, 0), (30, 2, 65, 1), (9, 7, 2305, 500)]
+          (16, 4, 2048, 0), (3, 5, 333, 77), (40, 4, 129, 0), (30, 2, 65, 1), (9, 7, 2305, 500), (20, 4, 700, 8)]
 
 
 @pytest.mark.parametrize("B,H,T,W", SHAPES)
