@@ -282,53 +282,6 @@ __device__ __forceinline__ void warp_store_32cols(uint32_t epi, int lane, const 
   }
 }
 
-// Same for 16 consecutive values per lane: rows of 64 bytes (fp32, eight rows per store instruction)
-// or 32 bytes (bf16, sixteen rows per instruction) through at most 2 KB of the warp's buffer.
-__device__ __forceinline__ void warp_store_16cols(uint32_t epi, int lane, const float (&v)[16], uint8_t* grow0,
-                                                  size_t row_stride_bytes, int rows_valid, int out_f32) {
-  if (out_f32) {
-    const uint32_t wsw = (lane >> 1) & 3u;
-#pragma unroll
-    for (uint32_t j = 0; j < 4; ++j)
-      sts128(epi + lane * 64u + ((j ^ wsw) << 4),
-             make_uint4(__float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]), __float_as_uint(v[4 * j + 2]),
-                        __float_as_uint(v[4 * j + 3])));
-    __syncwarp();
-    uint4 t[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t row = 8 * k + (lane >> 2), j = lane & 3;
-      t[k] = lds128(epi + row * 64u + ((j ^ ((row >> 1) & 3u)) << 4));
-    }
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int row = 8 * k + (lane >> 2), j = lane & 3;
-      if (row < rows_valid) *reinterpret_cast<uint4*>(grow0 + (size_t)row * row_stride_bytes + j * 16) = t[k];
-    }
-    __syncwarp();
-  } else {
-    const uint32_t wsw = (lane >> 2) & 1u;
-#pragma unroll
-    for (uint32_t j = 0; j < 2; ++j)
-      sts128(epi + lane * 32u + ((j ^ wsw) << 4),
-             make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                        pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7])));
-    __syncwarp();
-    uint4 t[2];
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const uint32_t row = 16 * k + (lane >> 1), j = lane & 1;
-      t[k] = lds128(epi + row * 32u + ((j ^ ((row >> 2) & 1u)) << 4));
-    }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int row = 16 * k + (lane >> 1), j = lane & 1;
-      if (row < rows_valid) *reinterpret_cast<uint4*>(grow0 + (size_t)row * row_stride_bytes + j * 16) = t[k];
-    }
-    __syncwarp();
-  }
-}
-
 // In-register inverse rotation of a full fp32 row (rope_bwd, ops.mojo:1119-1120):
 //   dx1 = dy1*c - dy2*s ; dx2 = dy1*s + dy2*c
 __device__ __forceinline__ void rope_bwd_pair(float& g1, float& g2, float c, float s) {
@@ -411,78 +364,6 @@ __device__ __forceinline__ void warp_store_pair16(uint32_t epi, int lane, const 
   }
 }
 
-
-// Write-out of two 32-column blocks A and B of an fp32 accumulator in tensor memory (this warp's
-// 32 lanes = 32 consecutive rows; block B lies 64 columns after A, i.e. the two hold the column
-// pairs (d, d+64) a rotation couples) to global memory, as fp32 or bf16, multiplied by `mul` and,
-// if cos_blk / sin_blk are given (tables [pos][64], already offset to block A's first column),
-// rotated back per row: rope_bwd, ops.mojo:1119-1120, with position min(row, T-1).  Needs 32
-// registers of payload: the rows leave 16 at a time - all lanes load a block from tensor memory,
-// the half-warp whose rows are due stages them (16-byte chunks XOR-swizzled by the row), then each
-// lane takes 16 bytes of A and of B of one row from the staging buffer (4 KB: 2 blocks x 16 rows x
-// 128 bytes), rotates and stores, so that an instruction writes four complete 128-byte lines (fp32;
-// 64-byte lines for bf16).  `free_bar` != 0: arrive there (lane 0) once the last tensor-memory
-// load of the call has completed, i.e. when the accumulator may be overwritten.
-__device__ __forceinline__ void store_block_pair(uint32_t epi, int lane, uint32_t tA, uint32_t tB, float mul,
-                                                 uint8_t* gA, uint8_t* gB, size_t row_stride_bytes, int rows_valid,
-                                                 int out_f32, const float* cos_blk, const float* sin_blk, int row0,
-                                                 int T, uint32_t free_bar) {
-#pragma unroll 1
-  for (int half = 0; half < 2; ++half) {
-    const bool mine = (lane >> 4) == half;
-    const uint32_t rl = lane & 15;
-#pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      uint32_t v[32];
-      tmem_ld32_wait(blk == 0 ? tA : tB, v);
-      if (blk == 1 && half == 1 && free_bar != 0u) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(free_bar);
-      }
-      if (mine) {
-#pragma unroll
-        for (uint32_t j = 0; j < 8; ++j)
-          sts128(epi + blk * 2048u + rl * 128u + ((j ^ (rl & 7u)) << 4),
-                 make_uint4(__float_as_uint(__uint_as_float(v[4 * j]) * mul), __float_as_uint(__uint_as_float(v[4 * j + 1]) * mul),
-                            __float_as_uint(__uint_as_float(v[4 * j + 2]) * mul), __float_as_uint(__uint_as_float(v[4 * j + 3]) * mul)));
-      }
-    }
-    __syncwarp();
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t r16 = 4 * k + (lane >> 3), j = lane & 7;   // row within the 16, 16-byte chunk
-      const int row = 16 * half + (int)r16;
-      uint4 a = lds128(epi + r16 * 128u + ((j ^ (r16 & 7u)) << 4));
-      uint4 b = lds128(epi + 2048u + r16 * 128u + ((j ^ (r16 & 7u)) << 4));
-      if (cos_blk != nullptr) {
-        const size_t pos = (size_t)min(row0 + row, T - 1);
-        const float4 cv = __ldg(reinterpret_cast<const float4*>(cos_blk + pos * 64) + j);
-        const float4 sv = __ldg(reinterpret_cast<const float4*>(sin_blk + pos * 64) + j);
-        float a0 = __uint_as_float(a.x), a1 = __uint_as_float(a.y), a2 = __uint_as_float(a.z), a3 = __uint_as_float(a.w);
-        float b0 = __uint_as_float(b.x), b1 = __uint_as_float(b.y), b2 = __uint_as_float(b.z), b3 = __uint_as_float(b.w);
-        rope_bwd_pair(a0, b0, cv.x, sv.x);
-        rope_bwd_pair(a1, b1, cv.y, sv.y);
-        rope_bwd_pair(a2, b2, cv.z, sv.z);
-        rope_bwd_pair(a3, b3, cv.w, sv.w);
-        a = make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3));
-        b = make_uint4(__float_as_uint(b0), __float_as_uint(b1), __float_as_uint(b2), __float_as_uint(b3));
-      }
-      if (row < rows_valid) {
-        if (out_f32) {
-          *reinterpret_cast<uint4*>(gA + (size_t)row * row_stride_bytes + j * 16) = a;
-          *reinterpret_cast<uint4*>(gB + (size_t)row * row_stride_bytes + j * 16) = b;
-        } else {
-          *reinterpret_cast<uint2*>(gA + (size_t)row * row_stride_bytes + j * 8) =
-              make_uint2(pack_bf16x2(__uint_as_float(a.x), __uint_as_float(a.y)), pack_bf16x2(__uint_as_float(a.z), __uint_as_float(a.w)));
-          *reinterpret_cast<uint2*>(gB + (size_t)row * row_stride_bytes + j * 8) =
-              make_uint2(pack_bf16x2(__uint_as_float(b.x), __uint_as_float(b.y)), pack_bf16x2(__uint_as_float(b.z), __uint_as_float(b.w)));
-        }
-      }
-    }
-    __syncwarp();
-  }
-}
 
 // Static schedule of a persistent kernel: round k hands the items [k*G, (k+1)*G) to the G CTAs, in
 // CTA order in even rounds and in reverse order in odd rounds, so that with items sorted by
