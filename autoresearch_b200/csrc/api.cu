@@ -563,7 +563,7 @@ static ar_status linear_call(int mode, void* out, const void* a_in, const void* 
   if (mode == 2) {   // split the long depth so that every SM has work; each chunk adds its partial tile
     const int tiles = ((p.rows_a + 127) / 128) * ((p.cols_b + 255) / 256);
     int chunks = (2 * 148 + tiles - 1) / tiles;
-    const int max_chunks = (p.depth + 1023) / 1024;
+    const int max_chunks = (p.depth + 511) / 512;
     if (chunks > max_chunks) chunks = max_chunks;
     if (chunks < 1) chunks = 1;
     p.depth_chunk = ((p.depth + chunks - 1) / chunks + 63) / 64 * 64;
