@@ -360,14 +360,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       g0 += wi.n_sub;
       if (!mbar_wait(w, smem_u32(&sm.acc_done), n & 1)) { ok = false; break; }
       tc_fence_after();
-      // Warpgroup 0 writes out dV, warpgroup 1 dK (scaled, rotated back).  The accumulator row goes
-      // to registers first, which frees tensor memory for the next item's accumulation.
+      // Warpgroup 0 writes out dV, warpgroup 1 dK (scaled, rotated back), 16 + 16 columns (a block and
+      // the block 64 columns on, which a rotation pairs) per pass of a loop that is NOT unrolled: code
+      // that runs once per item is fetched from far away (about 100 cycles per 128 bytes of it), so
+      // four passes through one small body cost less than one pass through a body four times the
+      // size.  The accumulator is released after the last pass has it in registers; the next item's
+      // first accumulation needs P^T / dS^T from these same warps and cannot start earlier anyway.
       const uint32_t acc = tmem + lane_off + (wg == 0 ? kColAcc0 : kColAcc1);
-      uint32_t a0[32], a1[32], b0[32], b1[32];   // columns [0,32) [32,64) | [64,96) [96,128)
-      tmem_ld32x2_wait(acc, a0, acc + 32, a1);
-      tmem_ld32x2_wait(acc + 64, b0, acc + 96, b1);
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sm.acc_free));
       const int esize = p.grad_f32 ? 4 : 2;
       const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
       const int wrow0 = row0 + 32 * (warp & 3);   // first row of this warp's 32-row block
@@ -376,29 +375,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       const int rows_valid = T - wrow0;
       const float mul = wg == 0 ? 1.f : p.scale * kTruncGainInv;   // dS carried the gain of P'
       const bool rot = wg == 1 && p.cos_buf != nullptr;
-      const int pos = min(row, T - 1);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float lo_v[32], hi_v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          lo_v[i] = __uint_as_float(c == 0 ? a0[i] : a1[i]) * mul;
-          hi_v[i] = __uint_as_float(c == 0 ? b0[i] : b1[i]) * mul;
+#pragma unroll 1
+      for (int cg = 0; cg < 4; ++cg) {
+        RotTable rt;
+        if (rot) rot_table_fetch(rt, p.cos_buf, p.sin_buf, wrow0, lane, 16 * cg, T);
+        uint32_t a[16], b[16];
+        tmem_ld16x2_wait(acc + 16 * cg, a, acc + 64 + 16 * cg, b);
+        if (cg == 3) {
+          tc_fence_before();
+          mbar_arrive(smem_u32(&sm.acc_free));
         }
-        if (rot) {
-          const float4* cp = reinterpret_cast<const float4*>(p.cos_buf + (size_t)pos * 64 + c * 32);
-          const float4* sp = reinterpret_cast<const float4*>(p.sin_buf + (size_t)pos * 64 + c * 32);
+        float lo_v[16], hi_v[16];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
-            rope_bwd_pair(lo_v[4 * i], hi_v[4 * i], cv.x, sv.x);
-            rope_bwd_pair(lo_v[4 * i + 1], hi_v[4 * i + 1], cv.y, sv.y);
-            rope_bwd_pair(lo_v[4 * i + 2], hi_v[4 * i + 2], cv.z, sv.z);
-            rope_bwd_pair(lo_v[4 * i + 3], hi_v[4 * i + 3], cv.w, sv.w);
-          }
+        for (int i = 0; i < 16; ++i) {
+          lo_v[i] = __uint_as_float(a[i]) * mul;
+          hi_v[i] = __uint_as_float(b[i]) * mul;
         }
-        warp_store_32cols(epi, lane, lo_v, gout + (size_t)(c * 32) * esize, row_stride, rows_valid, p.grad_f32);
-        warp_store_32cols(epi, lane, hi_v, gout + (size_t)(64 + c * 32) * esize, row_stride, rows_valid, p.grad_f32);
+        warp_store_pair16_rt(rot, epi, lane, lo_v, hi_v, rt, gout, row_stride, 16 * cg, rows_valid, p.grad_f32);
       }
       ++n;
     }

@@ -363,6 +363,55 @@ __device__ __forceinline__ void warp_store_pair16(uint32_t epi, int lane, const 
     __syncwarp();
   }
 }
+// The same with the rotation decided at run time (one copy of the code for rotated and plain rows).
+__device__ __forceinline__ void warp_store_pair16_rt(bool rot_on, uint32_t epi, int lane, const float (&lo)[16],
+                                                     const float (&hi)[16], const RotTable& rot, uint8_t* grow0,
+                                                     size_t row_stride_bytes, int col0, int rows_valid, int out_f32) {
+  const int esize = out_f32 ? 4 : 2;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if ((lane >> 4) == h) {
+      const uint32_t rl = lane & 15, wsw = (rl >> 1) & 3u;
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        sts128(epi + rl * 64u + ((j ^ wsw) << 4),
+               make_uint4(__float_as_uint(lo[4 * j]), __float_as_uint(lo[4 * j + 1]), __float_as_uint(lo[4 * j + 2]),
+                          __float_as_uint(lo[4 * j + 3])));
+        sts128(epi + 1024u + rl * 64u + ((j ^ wsw) << 4),
+               make_uint4(__float_as_uint(hi[4 * j]), __float_as_uint(hi[4 * j + 1]), __float_as_uint(hi[4 * j + 2]),
+                          __float_as_uint(hi[4 * j + 3])));
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t rl = 8 * k + (lane >> 2), j = lane & 3;
+      const uint32_t off = rl * 64u + ((j ^ ((rl >> 1) & 3u)) << 4);
+      const uint4 a = lds128(epi + off), b = lds128(epi + 1024u + off);
+      float x[4] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w)};
+      float y[4] = {__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w)};
+      if (rot_on) {
+        const float4 c = rot.c[h][k], s = rot.s[h][k];
+        rope_bwd_pair(x[0], y[0], c.x, s.x);
+        rope_bwd_pair(x[1], y[1], c.y, s.y);
+        rope_bwd_pair(x[2], y[2], c.z, s.z);
+        rope_bwd_pair(x[3], y[3], c.w, s.w);
+      }
+      const int row = 16 * h + (int)rl;
+      if (row < rows_valid) {
+        uint8_t* g = grow0 + (size_t)row * row_stride_bytes + (size_t)(col0 + 4 * j) * esize;
+        if (out_f32) {
+          *reinterpret_cast<float4*>(g) = make_float4(x[0], x[1], x[2], x[3]);
+          *reinterpret_cast<float4*>(g + 64 * 4) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+          *reinterpret_cast<uint2*>(g) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+          *reinterpret_cast<uint2*>(g + 64 * 2) = make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
 
 
 // Static schedule of a persistent kernel: round k hands the items [k*G, (k+1)*G) to the G CTAs, in
