@@ -551,17 +551,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const uint32_t lane_off = static_cast<uint32_t>(wq * 32) << 16;
       const uint32_t epi = smem_u32(sm.epi[wq]);
       const uint32_t wbase = epi + lane * 128u, sw = lane & 7u;
-      int nxe[2] = {0, 0};
+      int nxe0 = 0, nxe1 = 0;
       bool ok = true;
       for (int kk = 0; ok; ++kk) {
         const int item = sched_item(kk, n_items);
         if (item == -1) break;
         if (item == -2) continue;
         const FwdItem wi = fwd_item(item, p.dims, n_qb);
-#pragma unroll
+        // Neither loop is unrolled: this code runs once per tile and item, and code that is not
+        // resident costs about 100 cycles per 128 bytes of it to fetch, so one small body run
+        // eight times is cheaper than eight copies run once.
+#pragma unroll 1
         for (int X = 0; X < 2; ++X) {
           if (!(X == 0 ? wi.act[0] : wi.act[1])) continue;
-          const int ph = (X == 0 ? nxe[0] : nxe[1]) & 1;
+          const int ph = (X == 0 ? nxe0 : nxe1) & 1;
           if (!mbar_wait(w, smem_u32(&sm.stat_ready[X]), ph)) { ok = false; break; }
           const float* stat = reinterpret_cast<const float*>(sm.epi[4]) + X * 256;
           const float l_row = stat[r] * kTruncGainInv;   // the row sum was accumulated from the inflated P
@@ -575,7 +578,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           const size_t row_stride = (size_t)p.dims.pitch_t * 128 * esize;
           const int wrow0 = qlo + 32 * wq;   // first row of this warp's 32-row block
           uint8_t* gout = static_cast<uint8_t*>(p.o) + row_of(p.dims, wi.b, wrow0, wi.h) * 128 * esize;
-#pragma unroll
+#pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t og[32];
             tmem_ld32_wait(tO + c * 32, og);
@@ -614,7 +617,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             }
           }
           if (qrow < T) p.lse[row_of(p.dims, wi.b, qrow, wi.h)] = m_row * p.scale + logf(l_row);
-          if (X == 0) ++nxe[0]; else ++nxe[1];
+          if (X == 0) ++nxe0; else ++nxe1;
         }
       }
     } else {
