@@ -49,7 +49,7 @@ C5 = dict(B=128, H=8, T=2048, windows=(1024, 1024, 1024, 2048))       # BASELINE
 # DRAM bytes per launch (dram__bytes_read.sum, dram__bytes_write.sum) from an ncu capture of
 # full-size launches: B=16, H=4, T=2048, W=1024, 64 (b,h) units; other unit counts scale it.
 NCU_DRAM = {
-    "attn_fwd": (126.8e6, 9.9e6), "attn_bwd_dq": (265.3e6, 38.2e6), "attn_bwd_dkv": (157.0e6, 79.2e6),
+    "attn_fwd": (131.9e6, 10.1e6), "attn_bwd_dq": (285.1e6, 55.6e6), "attn_bwd_dkv": (159.1e6, 83.3e6),
     "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:attn_ "
               "-s 36 -c 12 on `bench.py --steps 2 --warmup 3 --no-e2e --no-cpu --no-sustained --no-config5 "
               "--no-phases` (B=16 H=4 T=2048; mean of the three W=1024 launches of each kernel; "
@@ -346,6 +346,22 @@ def run_gpu(args):
     step_fl = flops(14, T, windows, B, H)
     value = step_fl * world / (ms_step * 1e-3) / 1e12
     line_extra = {}
+
+    # ---- the same step with bf16 gradients (what a torch caller of bf16 tensors gets back) -------
+    # The headline keeps the reference's fp32 gradient tensors; this is the same work with half the
+    # gradient bytes written.
+    if not args.no_phases:
+        glayers = [make_layer(B, T, H, w, grad_dtype=torch.bfloat16) for w in windows]
+        gstep = make_step(glayers)
+        for _ in range(3):
+            gstep()
+        barrier()
+        ms_g = max_over_ranks(timed(gstep, args.steps)) / args.steps
+        line_extra["bf16_gradients"] = {"value": step_fl * world / (ms_g * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                        "ms_per_step": ms_g, "note": "dQ, dK, dV written as bf16 instead of fp32 (through a write-out laid out for "
+                                                "fp32 rows: the bf16 rows leave in 32-byte pieces)"}
+        del glayers, gstep
+        check_status()
 
     # ---- config 4 only: the full causal mask, timed the same way -----------------------------
     if args.config == 4:

@@ -188,7 +188,10 @@ AR_API ar_status ar_flash_attn_bwd_dkv(float* grad_k, float* grad_v, const float
  * the library's scratch) for both inputs, out_dtype for the result.  All matrices row-major and
  * contiguous; N and K multiples of 8, the result's row length a multiple of 32; M arbitrary.
  * What the reference's docstrings state is computed (its kernels write only a quarter of each
- * output tile, ops.mojo:134-143).
+ * output tile, ops.mojo:134-143).  With AR_F32 operands the output may be one of the inputs
+ * (they are staged first: the in-place call at model.mojo:906 works as written); with AR_BF16
+ * operands an aliased output is refused.  The scratch of the AR_F32 form is the same
+ * per-device block the mirrors under (i) use: one thread and one stream per device at a time.
  * ------------------------------------------------------------------------------------ */
 
 /* replaces linear_fwd (ops.mojo:110-117; launch_linear, model.mojo:162-174):
