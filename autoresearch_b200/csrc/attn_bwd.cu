@@ -301,8 +301,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           }
         }
         // Two-lane fp32 arithmetic throughout; P' = kTruncGain * P is truncated to bf16 (the gain
-        // makes the truncation unbiased, see ptx.cuh), dS' = P' * (dP - D) is rounded; three pairs
-        // in eight take the polynomial exp2 so that the special-function unit is not the bound.
+        // makes the truncation unbiased, see ptx.cuh), dS' = P' * (dP - D) is rounded; every
+        // exponential is an ex2.approx.
         uint32_t pp[16], pd[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -312,20 +312,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           for (int e = 0; e < 2; ++e) {
             const int j = 4 * i + 2 * e;
             const f32x2 x = f2_fma(f2_pack_u(sr[j], sr[j + 1]), sc2, nl[e]);
-            float p0, p1;
-            const int q8 = (2 * i + e) & 7;
-            if (q8 == 1 || q8 == 4 || q8 == 6) {
-              ex2_poly2(x, p0, p1);
-            } else {
-              float x0, x1;
-              f2_unpack(x, x0, x1);
-              p0 = ex2_approx(x0);
-              p1 = ex2_approx(x1);
-            }
+            float x0, x1;
+            f2_unpack(x, x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
             float s0, s1;
             f2_unpack(f2_mul(f2_pack(p0, p1), f2_sub(f2_pack_u(dr[j], dr[j + 1]), dd[e])), s0, s1);
             pp[2 * i + e] = pack_bf16x2_trunc(p0, p1);
-            pd[2 * i + e] = pack_bf16x2_alu(s0, s1);
+            pd[2 * i + e] = pack_bf16x2(s0, s1);
             if (kMayTwo) {   // kept for the second pass of a two-term sub-tile
               sr[j] = __float_as_uint(p0);
               sr[j + 1] = __float_as_uint(p1);

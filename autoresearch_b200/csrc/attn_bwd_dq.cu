@@ -415,24 +415,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (i < lo) sr[i] = 0xff800000u;
         }
         // dS' = P' (dP - D) with P' = kTruncGain * 2^(s*scale*log2e - lse*log2e), rounded to bf16 (the
-        // gain is divided out at the write-out); two-lane fp32 arithmetic, and three pairs in eight
-        // take the polynomial exp2 to relieve the special-function unit.
+        // gain is divided out at the write-out); two-lane fp32 arithmetic, every exponential an
+        // ex2.approx.
         uint32_t pd[kDqCols / 2], pl[kDqCols / 2];
 #pragma unroll
         for (int i = 0; i < kDqCols / 2; ++i) {
           const f32x2 x = f2_fma(f2_pack_u(sr[2 * i], sr[2 * i + 1]), sc2, nl2);
-          float p0, p1;
-          if ((i & 7) == 1 || (i & 7) == 4 || (i & 7) == 6) {
-            ex2_poly2(x, p0, p1);
-          } else {
-            float x0, x1;
-            f2_unpack(x, x0, x1);
-            p0 = ex2_approx(x0);
-            p1 = ex2_approx(x1);
-          }
+          float x0, x1;
+          f2_unpack(x, x0, x1);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
           float s0, s1;
           f2_unpack(f2_mul(f2_pack(p0, p1), f2_sub(f2_pack_u(dr[2 * i], dr[2 * i + 1]), dd2)), s0, s1);
-          pd[i] = pack_bf16x2_alu(s0, s1);
+          pd[i] = pack_bf16x2(s0, s1);
           if (kMayTwo)   // the rounding residual dS - bf16(dS), exact in fp32
             pl[i] = pack_bf16x2_alu(s0 - bf16_lo_to_f32(pd[i]), s1 - bf16_hi_to_f32(pd[i]));
         }

@@ -266,10 +266,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         } else {
           if (it < n_other && !counter_wait(w, smem_u32(&sm.exp_cnt[0]), 4u * (uint32_t)(g_oth + it + 1))) { ok = false; break; }
         }
-        // P = 2^(s*scale*log2e - m*scale*log2e) * kTruncGain, truncated to bf16 (see ptx.cuh).
-        // Three pairs in eight take the polynomial path (FMA pipe), five the special-function
-        // unit, which at 16 results per clock per SM would otherwise need as long for a tile as
-        // the tensor pipe does.  Each 64-key half is handed to the issuer as soon as it is written.
+        // P = 2^(s*scale*log2e - m*scale*log2e) * kTruncGain, truncated to bf16 (see ptx.cuh).  Every
+        // exponential is an ex2.approx: the special-function unit sustains about 31 per clock per SM
+        // (rate probe), which is not what bounds this loop, and moving a share of them to a cubic on
+        // the FMA pipe (tried at 1/8, 2/8, 3/8) only adds instructions.  Each 64-key half is handed to
+        // the issuer as soon as it is written.
         const float neg_ms = ((m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2e) + kTruncGainLog2;
         const f32x2 nm2 = f2_pack(neg_ms, neg_ms);
         f32x2 sum_a = 0ull, sum_b = 0ull;   // two lanes of +0.0f each
@@ -279,15 +280,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const f32x2 x = f2_fma(f2_pack_u(sr[c * 64 + 2 * i], sr[c * 64 + 2 * i + 1]), sc2, nm2);
-            float p0, p1;
-            if ((i & 7) == 1 || (i & 7) == 4 || (i & 7) == 6) {
-              ex2_poly2(x, p0, p1);
-            } else {
-              float x0, x1;
-              f2_unpack(x, x0, x1);
-              p0 = ex2_approx(x0);
-              p1 = ex2_approx(x1);
-            }
+            float x0, x1;
+            f2_unpack(x, x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
             if (i & 1) sum_b = f2_add(sum_b, f2_pack(p0, p1));
             else sum_a = f2_add(sum_a, f2_pack(p0, p1));
             pk[i] = pack_bf16x2_trunc(p0, p1);

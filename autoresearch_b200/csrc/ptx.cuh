@@ -460,8 +460,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 // bf16x2 packing on the integer pipe: round the magnitude half-up (add 0x8000) and keep the high
 // halves (one PRMT).  Narrowing float conversions (cvt.rn.bf16x2.f32, cvt.rn.f16x2.f32) issue on
-// the same quarter-rate unit as ex2, and the hot loops of all three attention kernels are bound by
-// that unit; this form differs from round-to-nearest-even only on exact ties.  (Packed f16x2
+// the same special-function unit as ex2; this form differs from round-to-nearest-even only on exact ties.  (Packed f16x2
 // exponentials were measured too: the f32 -> f16x2 conversion they need costs what they save.)
 __device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
   return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
@@ -525,28 +524,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-// 2^x for two values on the FMA pipe instead of the 16-per-clock special-function unit:
-// x = j + f with j = round(x) (magic-number addition), f in [-0.5, 0.5]; a cubic for 2^f (relative
-// error < 7.5e-5, far below the bf16 rounding the result meets next) whose exponent field is then
-// raised by j with one integer add.  x is clamped at -126, so -inf (a masked score) gives 2^-126.
-__device__ __forceinline__ void ex2_poly2(f32x2 x, float& r0, float& r1) {
-  float x0, x1;
-  f2_unpack(x, x0, x1);
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const f32x2 xc = f2_pack(x0, x1);
-  const f32x2 magic = f2_pack(12582912.f, 12582912.f);   // 1.5 * 2^23
-  const f32x2 t = f2_add(xc, magic);
-  const f32x2 fr = f2_sub(xc, f2_sub(t, magic));
-  f32x2 p = f2_fma(f2_pack(0.0551716685f, 0.0551716685f), fr, f2_pack(0.2426111251f, 0.2426111251f));
-  p = f2_fma(p, fr, f2_pack(0.6932609677f, 0.6932609677f));
-  p = f2_fma(p, fr, f2_pack(0.9999280572f, 0.9999280572f));
-  float p0, p1, t0, t1;
-  f2_unpack(p, p0, p1);
-  f2_unpack(t, t0, t1);
-  r0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-  r1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 __device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) {
   return __uint_as_float(packed << 16);
