@@ -49,7 +49,7 @@ C5 = dict(B=128, H=8, T=2048, windows=(1024, 1024, 1024, 2048))       # BASELINE
 # DRAM bytes per launch (dram__bytes_read.sum, dram__bytes_write.sum) from an ncu capture of
 # full-size launches: B=16, H=4, T=2048, W=1024, 64 (b,h) units; other unit counts scale it.
 NCU_DRAM = {
-    "attn_fwd": (131.9e6, 10.1e6), "attn_bwd_dq": (285.1e6, 55.6e6), "attn_bwd_dkv": (159.1e6, 83.3e6),
+    "attn_fwd": (126.5e6, 8.8e6), "attn_bwd_dq": (276.3e6, 50.3e6), "attn_bwd_dkv": (157.9e6, 83.1e6),
     "source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:attn_ "
               "-s 36 -c 12 on `bench.py --steps 2 --warmup 3 --no-e2e --no-cpu --no-sustained --no-config5 "
               "--no-phases` (B=16 H=4 T=2048; mean of the three W=1024 launches of each kernel; "
